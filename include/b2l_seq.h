@@ -42,9 +42,11 @@ int b2l_seq_rmsnorm(const float* x, const void* w, float eps, void* out, const i
 int b2l_seq_norm_add_norm(const void* y, const void* w_post, float eps, float* x, const void* w_next, void* h, int T,
                           int D, int act_dtype, b2l_stream_t stream);
 
-/* out[t, j] = act(gu[t, j]) * gu[t, F + j]  (gated feed-forward, both halves from one product). */
-enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2 };
-int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, int act_dtype, b2l_stream_t stream);
+/* out[t, j] = act(gu[t, j]) * gu[t, F + j]  (gated feed-forward, both halves from one product).
+ * B2L_SEQ_ACT_CLAMPED_SWISH is a gated unit with clamped halves: g = min(gu[t, j], limit),
+ * u = clamp(gu[t, F + j], -limit, limit), out = g * sigmoid(1.702 g) * (u + 1).  `limit` is read by it alone. */
+enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2, B2L_SEQ_ACT_CLAMPED_SWISH = 3 };
+int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, float limit, int act_dtype, b2l_stream_t stream);
 
 /* Short causal convolution over time per channel, then silu, with the last taps-1 inputs of the sequence carried
  * in `state` ([n_slots][taps-1][C] act, oldest first; a fresh slot holds zeros):
@@ -107,12 +109,14 @@ int b2l_seq_headnorm_rope(const void* x, int ldx, const void* w, float eps, cons
                           float rot_mult, const int* meta, void* out, int out_f32, int T, int heads, int size,
                           int act_dtype, b2l_stream_t stream);
 
-/* Block-local causal softmax attention with a sink: query at position p sees the keys j <= p with
- * j / block == p / block; score s = softcap * tanh(q.k * scale / softcap) (softcap <= 0: none); weights
- * exp(s_j) / (sink + sum exp(s_j)) with sink = 1 (has_sink) or 0; head h's output is multiplied by
- * sigmoid(gate[t, h]) when gate is given.  Keys of this portion come from k_new / v_new, older ones of the same
- * block from the ring cache ([n_slots][block][kv_heads][K or V] act, entry p % block).  After the call the ring
- * holds the portion's tokens that share the last token's block. */
+/* Local causal softmax attention.  window == 0 (block-local): the query at position p sees the keys j <= p with
+ * j / block == p / block.  window > 0 (sliding window): it sees the keys p - window + 1 .. p, and `block` (>= window)
+ * is only the size of the ring.  Score s = softcap * tanh(q.k * scale / softcap) (softcap <= 0: none); weights
+ * exp(s_j) / (sink + sum exp(s_j)) with sink = 1 (has_sink) or 0 (ordinary softmax); when gate is given head h's
+ * output is multiplied by sigmoid(gate[t, h]), or channel c of it by sigmoid(gate[t, h*V + c]) (gate_per_channel).
+ * Keys of this portion come from k_new / v_new, older ones from the ring cache ([n_slots][block][kv_heads][K or V]
+ * act, entry p % block).  After the call the ring holds the portion's tokens that share the last token's block
+ * (block-local) or its last `block` tokens (sliding window). */
 typedef struct {
   const float* q;                 /* f32 [T, heads*K], normalised and rotated */
   const void* k_new;              /* act [T, kv_heads*K], normalised and rotated */
@@ -123,6 +127,8 @@ typedef struct {
   void* out; int ldo;             /* act [T, ldo] */
   float scale, softcap, out_mult;  /* out_mult scales the output (a mixing weight of a parallel branch) */
   int has_sink, block, T, heads, kv_heads, K, V, act_dtype;
+  int window;                     /* 0: block-local; > 0: sliding window of that many positions */
+  int gate_per_channel;           /* gate is [T, heads*V] instead of [T, heads] */
 } b2l_seq_attn_args;
 int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
 
@@ -194,35 +200,85 @@ int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t str
 int b2l_seq_latent_attention_warps(int T, int heads_per_group);    /* warps per CTA that own rows: 4 rows per warp */
 
 /* ---- mixture of experts ----
- * Router, per token, from f32 logits [T, ld] over n experts: s = softmax(logits); choice = s + correction (f32 [n],
- * may be null); the n experts form `groups` equal groups of neighbours, a group's score is its largest choice score,
- * only experts of the `keep` best groups can be chosen; idx[t, :] = the `top` largest choice scores among them (best
- * first), weights[t, k] = s[idx] / (sum of the chosen s + 1e-20). */
-int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int* idx,
-                      float* weights, int T, b2l_stream_t stream);
+ * Router, per token, from f32 logits [T, ld] over n experts: s = softmax(logits) over the experts, or sigmoid(logits)
+ * of each (score_fn); choice = s + correction (f32 [n], may be null); the n experts form `groups` equal groups of
+ * neighbours, a group's score is its largest choice score, only experts of the `keep` best groups can be chosen;
+ * idx[t, :] = the `top` largest choice scores among them (best first, ties to the lower index);
+ * weights[t, k] = s[idx] / (sum of the chosen s + 1e-20) when `renormalize`, else s[idx] itself. */
+enum { B2L_SEQ_SCORE_SOFTMAX = 0, B2L_SEQ_SCORE_SIGMOID = 1 };
+int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int score_fn,
+                      int renormalize, int* idx, float* weights, int T, b2l_stream_t stream);
 
 /* The same with the logits computed in the kernel, for a few tokens: logits[t] = w_router h[t] (w_router act [n][D],
  * f32 accumulation), one CTA per token, one launch for product and routing. */
 int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups, int keep,
-                            int top, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream);
+                            int top, int score_fn, int renormalize, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream);
 
-/* Experts of a few tokens, indices read on the device.  Expert e < n_real: W_down[e] (silu(W_gate[e] h) * (W_up[e] h))
- * with w_gate_up act [n_real][2*ff][D] (gate rows, then up rows) and w_down act [n_real][D][ff]; e >= n_real: h itself.
- * y[t] = sum_k weights[t, k] * expert_idx[t,k](h[t]).  mid: act [T*top, ff] scratch. */
+/* Experts of a few tokens, indices read on the device.  Expert e < n_real: W_down[e] (gated(W_gate[e] h, W_up[e] h))
+ * with w_gate_up act [n_real][2*ff][D] (gate rows, then up rows), w_down act [n_real][D][ff] and the gated unit of
+ * b2l_seq_gated_act (`act`, `limit`); e >= n_real: h itself.
+ * y[t] = sum_k weights[t, k] * expert_idx[t,k](h[t]), or, with weight_input, sum_k expert_idx[t,k](weights[t, k] * h[t])
+ * (the weighted input passes through the storage type).  mid: act [T*top, ff] scratch. */
 int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_gate_up, const void* w_down, const int* idx,
                               const float* weights, void* mid, void* y, int ldy, int T, int D, int ff, int n_real, int top,
-                              int act_dtype, b2l_stream_t stream);
+                              int act, float limit, int weight_input, int act_dtype, b2l_stream_t stream);
 
 /* Long portions: the N = T*top assignments a = t*top + k sorted by expert.  offsets int32[n_real + 1]: expert e owns
  * the sorted places offsets[e] .. offsets[e+1]-1; perm[p] = assignment at place p; inv[a] = place of assignment a
  * (-1: an identity expert).  cursor: int32[n_real + 1] scratch. */
 int b2l_seq_moe_sort(const int* idx, int N, int n_real, int* offsets, int* cursor, int* perm, int* inv, b2l_stream_t stream);
-/* xg[p, :] = h[perm[p] / top, :] for p < *n_rows (device int32: offsets[n_real]); launched over N rows. */
-int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const int* n_rows, int top, void* xg, int N, int D,
-                       int act_dtype, b2l_stream_t stream);
-/* y[t] = sum_k weights[t, k] * (inv[a] >= 0 ? yg[inv[a]] : h[t]). */
+/* xg[p, :] = h[perm[p] / top, :] (times row_scale[perm[p]] when row_scale, f32 [N], is given: the router's weight on
+ * an expert's input) for p < *n_rows (device int32: offsets[n_real]); launched over N rows. */
+int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const int* n_rows, const float* row_scale, int top, void* xg, int N,
+                       int D, int act_dtype, b2l_stream_t stream);
+/* y[t] = sum_k weights[t, k] * (inv[a] >= 0 ? yg[inv[a]] : h[t]); weights null: every weight is 1. */
 int b2l_seq_moe_combine(const void* yg, const int* inv, const float* weights, const void* h, int ldh, void* y, int ldy, int T,
                         int D, int top, int act_dtype, b2l_stream_t stream);
+
+/* ---- several residual streams, token-pair embedding, attention operands ----
+ * Token embedding plus a hashed token-pair embedding, written into `streams` equal residual streams x [T][streams][D]:
+ *   x[t, s, :] = table[token[t]] * scale + pair_table[row(t)],
+ *   row(t) = (previous token * mul_prev + token[t] * mul_cur) mod buckets; the sequence's first token (position 0)
+ *   reads row `buckets`, the table's last.  pair_table null: the token embedding alone.
+ * prev_state: int32 [n_slots], the last token of every sequence (read for the portion's first token when pos0 > 0,
+ * then set to the portion's last token). */
+int b2l_seq_embed_pair(const void* tokens, int tokens_i64, const void* table, const void* pair_table, float scale, int* prev_state,
+                       const int* meta, long long mul_prev, long long mul_cur, int buckets, float* x, int T, int D, int vocab,
+                       int streams, int act_dtype, b2l_stream_t stream);
+
+/* One sublayer's step on S residual streams X [rows][S][D] (f32):
+ *   y given (act [rows, D], with mix f32 [S][S] indexed [from][to] and out_w f32 [S]):
+ *       X_t <- sum_s mix[s, t] X_s + out_w[t] y    for all t at once from the old streams;
+ *   w_next given (act [D], with in_next f32 [S] and h act [n_rows, D]):
+ *       h = u / sqrt(mean(u^2) + eps) * w_next,  u = sum_s in_next[s] X_s   (of the new streams).
+ * `rows` (device int32 [n_rows], may be null, only without y) picks the rows that are read: h row r <- X row rows[r].
+ * With S = 1, mix = out_w = in_next = 1 this is the ordinary residual step fused with the next pre-norm. */
+int b2l_seq_hc_step(const void* y, float* X, const float* mix, const float* out_w, const float* in_next, const void* w_next, void* h,
+                    float eps, const int* rows, int n_rows, int D, int streams, int act_dtype, b2l_stream_t stream);
+/* out[t, :] = sum_s X[t, s, :]. */
+int b2l_seq_hc_sum(const float* X, float* out, int T, int D, int streams, b2l_stream_t stream);
+
+/* z <- z * mult in place on f32 (a constant scale of the logits). */
+int b2l_seq_scale(float* z, size_t n, float mult, b2l_stream_t stream);
+
+/* Attention operands from one stacked projection row proj[t] (act [T, ld]) with q at q_off (heads x K), k at k_off
+ * (kv_heads x K) and v at v_off (kv_heads x V):
+ *   q_out (f32 [T, heads*K]), k_out (act [T, kv_heads*K]): RMS norm with eps (whole_row: over all entries of the
+ *   projection at once, weight of heads*K resp. kv_heads*K entries; else per head, weight of K entries shared by the
+ *   heads; null weight: no norm), then rotation of the first rot_dims entries of each head (entry i with entry
+ *   i + rot_dims/2) by the angle (pos0 + t) * freq[i], cos and sin multiplied by rot_mult;
+ *   v_out (act [T, kv_heads*V]) = (1 - lambda) v + lambda v_first when v_first (act [T, ldvf]) is given; lambda is a
+ *   device scalar (act).  Without v_first nothing is written to v_out. */
+typedef struct {
+  const void* proj; int ld; int q_off, k_off, v_off;
+  const void* q_norm; const void* k_norm; int whole_row; float eps;
+  const float* freq; int rot_dims; float rot_mult;
+  const int* meta;
+  float* q_out; void* k_out;
+  const void* v_first; int ldvf; const void* lambda; void* v_out;
+  int T, heads, kv_heads, K, V, act_dtype;
+} b2l_seq_qkv_prep_args;
+int b2l_seq_qkv_prep(const b2l_seq_qkv_prep_args* a, b2l_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -18,9 +18,9 @@ LIBRARIES = {
     "llama": dict(out=os.path.join(PKG, "libb200llama.so"),
                   sources=["api.cu", "q_generic.cu", "elementwise.cu", "attention.cu", "q4_tc.cu", "q4_gemv.cu", "q4_gemv_batch.cu",
                            "q8_gemv.cu", "sampling.cu", "decode_mega.cu", "q4_gemm.cu", "tp_allreduce.cu"]),
-    # sequence-mixer kernels: recurrences, block-local and latent attention, expert routing, f32 residual stream (include/b2l_seq.h)
+    # sequence-mixer kernels: recurrences, local and latent attention, expert routing, f32 residual streams (include/b2l_seq.h)
     "seq": dict(out=os.path.join(PKG, "libb200seq.so"),
-                sources=["seq_api.cu", "seq_elementwise.cu", "seq_scan.cu", "seq_attention.cu", "seq_latent.cu", "seq_moe.cu"]),
+                sources=["seq_api.cu", "seq_elementwise.cu", "seq_scan.cu", "seq_attention.cu", "seq_latent.cu", "seq_moe.cu", "seq_streams.cu"]),
 }
 
 

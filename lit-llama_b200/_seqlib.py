@@ -8,7 +8,8 @@ import torch
 from . import _build
 
 B2L_BF16, B2L_F32 = 0, 1
-ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID = 0, 1, 2
+ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_CLAMPED_SWISH = 0, 1, 2, 3
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 DECAY_EXP_SOFTPLUS, DECAY_SIGMOID_ROOT = 0, 1
 
 c_void_p, c_int, c_float, c_size_t = C.c_void_p, C.c_int, C.c_float, C.c_size_t
@@ -43,6 +44,7 @@ class AttnArgs(C.Structure):
         ("scale", c_float), ("softcap", c_float), ("out_mult", c_float),
         ("has_sink", c_int), ("block", c_int), ("T", c_int), ("heads", c_int), ("kv_heads", c_int), ("K", c_int), ("V", c_int),
         ("act_dtype", c_int),
+        ("window", c_int), ("gate_per_channel", c_int),
     ]
 
 
@@ -62,13 +64,25 @@ class LatentAttnArgs(C.Structure):
     ]
 
 
+class QkvPrepArgs(C.Structure):
+    _fields_ = [
+        ("proj", c_void_p), ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int),
+        ("q_norm", c_void_p), ("k_norm", c_void_p), ("whole_row", c_int), ("eps", c_float),
+        ("freq", c_void_p), ("rot_dims", c_int), ("rot_mult", c_float),
+        ("meta", c_void_p),
+        ("q_out", c_void_p), ("k_out", c_void_p),
+        ("v_first", c_void_p), ("ldvf", c_int), ("lambda_", c_void_p), ("v_out", c_void_p),
+        ("T", c_int), ("heads", c_int), ("kv_heads", c_int), ("K", c_int), ("V", c_int), ("act_dtype", c_int),
+    ]
+
+
 _SIGS = {
     "b2l_seq_version": (c_int, []),
     "b2l_seq_last_error": (C.c_char_p, []),
     "b2l_seq_embed": (c_int, [c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_rmsnorm": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_norm_add_norm": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
-    "b2l_seq_gated_act": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_gated_act": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "b2l_seq_conv_silu": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_void_p]),
     "b2l_seq_unit_norm": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
@@ -92,14 +106,21 @@ _SIGS = {
                                     c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_latent_attention": (c_int, [C.POINTER(LatentAttnArgs), c_void_p]),
     "b2l_seq_latent_attention_warps": (c_int, [c_int, c_int]),
-    "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
-    "b2l_seq_moe_route_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                        c_void_p]),
+    "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "b2l_seq_moe_route_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        c_int, c_int, c_void_p]),
     "b2l_seq_moe_experts_small": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                          c_int, c_int, c_int, c_int, c_void_p]),
+                                          c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
     "b2l_seq_moe_sort": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "b2l_seq_moe_gather": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_moe_gather": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_embed_pair": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, C.c_longlong, C.c_longlong, c_int, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_hc_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int,
+                                c_int, c_void_p]),
+    "b2l_seq_hc_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_scale": (c_int, [c_void_p, c_size_t, c_float, c_void_p]),
+    "b2l_seq_qkv_prep": (c_int, [C.POINTER(QkvPrepArgs), c_void_p]),
 }
 
 EXPORTS = tuple(_SIGS)

@@ -1,8 +1,8 @@
-// Block-local causal softmax attention with a sink term, score soft-capping, grouped key/value heads, a per-head
-// sigmoid output gate and a ring cache of one block of positions.
-//
-// A query at position p sees keys j <= p with j / block == p / block, so a sequence never needs more than `block`
-// cached positions: entry p % block of the ring.  Keys of the portion being processed are read from the fresh
+// Local causal softmax attention with an optional sink term, score soft-capping, grouped key/value heads, a sigmoid
+// output gate (one per head or one per channel) and a ring cache of `block` positions.  Two kinds of locality:
+//   block-local (window == 0): a query at position p sees keys j <= p with j / block == p / block;
+//   sliding window (window > 0): it sees the keys p - window + 1 .. p (itself and the window - 1 positions before it).
+// Either way a sequence never needs more than `block` cached positions: entry p % block of the ring.  Keys of the portion being processed are read from the fresh
 // projections (k_new / v_new), older ones of the same block from the ring; the ring is advanced AFTER the
 // attention kernel (a second kernel in the same call), so a portion longer than a block cannot overwrite what it
 // still has to read.
@@ -15,6 +15,11 @@
 namespace b2l {
 
 constexpr int ATT_VMAX = 8;   // value channels per lane: V <= 256
+
+// The first position a query at position p sees.
+__device__ __forceinline__ int first_visible(const b2l_seq_attn_args& a, int p) {
+  return a.window > 0 ? max(0, p - a.window + 1) : (p / a.block) * a.block;
+}
 
 template <typename act_t>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const act_t* __restrict__ k, int K, bool vec);
@@ -68,7 +73,7 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
   const int t = live ? pair / a.heads : 0, h = live ? pair % a.heads : 0;
   const int g = h / (a.heads / a.kv_heads);
   const int slot = a.meta[0], pos0 = a.meta[1];
-  const int p = pos0 + t, c0 = (p / a.block) * a.block;       // first position of p's block
+  const int p = pos0 + t, c0 = first_visible(a, p);
 
   float* myq = sq + (warp / WPQ) * Kpad;
   if (live && sub == 0)
@@ -91,7 +96,7 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
       float s = -INFINITY;
       if (j <= p) {
         const act_t* kr = j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K
-                                    : ck + ((size_t)(j - c0) * a.kv_heads + g) * K;
+                                    : ck + ((size_t)(j % a.block) * a.kv_heads + g) * K;
         s = dot_row<act_t>(myq, kr, K, vec != 0) * a.scale;
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
       }
@@ -108,7 +113,7 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
         const float wj = __shfl_sync(0xffffffffu, w, jj);      // 0 beyond the last key of the batch
         const int jv = jb + min(jj, nb - 1);                    // a valid row for the masked tail (weight 0)
         const act_t* vr = jv >= pos0 ? vn + (size_t)(jv - pos0) * a.ldv + (size_t)g * V
-                                     : cv + ((size_t)(jv - c0) * a.kv_heads + g) * V;
+                                     : cv + ((size_t)(jv % a.block) * a.kv_heads + g) * V;
 #pragma unroll
         for (int c = 0; c < ATT_VMAX; ++c) {
           const int ch = c * 32 + lane;
@@ -140,12 +145,13 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
   }
   if (!live) return;
   float f = a.out_mult / l;
-  if (a.gate) f *= sigmoid_f(ld_act((const act_t*)a.gate, (size_t)t * a.ldg + h));
+  const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
+  if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
   act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
 #pragma unroll
   for (int c = 0; c < ATT_VMAX; ++c) {
     const int ch = c * 32 + lane;
-    if (ch < V) st_act(o, ch, acc[c] * f);
+    if (ch < V) st_act(o, ch, acc[c] * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
   }
 }
 
@@ -178,7 +184,7 @@ template <typename act_t, int VC>
 __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(b2l_seq_attn_args a) {
   extern __shared__ __align__(16) float smem[];
   constexpr int PER = 16 / (int)sizeof(act_t);            // elements per 16 bytes
-  const int K = a.K, V = 32 * VC, Kp = K + 4, Kpa = K + PER;
+  const int K = a.K, V = a.V, Kp = K + 4, Kpa = K + PER;    // 32 (VC - 1) < V <= 32 VC, V a multiple of 4
   float* sQ = smem;                                       // [TQ][Kp] f32
   float* sP = sQ + TQ * Kp;                               // [TQ][TK + 1]
   act_t* sKb = reinterpret_cast<act_t*>(sP + TQ * (TK + 1) + 3);   // 2 x [TK][Kpa]
@@ -190,7 +196,8 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
   const int t_first = qt * TQ, nq = min(TQ, a.T - t_first);
   const int slot = a.meta[0], pos0 = a.meta[1];
   const int p_first = pos0 + t_first, p_last = p_first + nq - 1;
-  const int j_begin = (p_first / a.block) * a.block;
+  const int j_begin = first_visible(a, p_first);
+  const bool vlast = tx * 4 + 32 * (VC - 1) < V;          // this thread's last group of 4 value channels exists
 
   const act_t* kn = (const act_t*)a.k_new;
   const act_t* vn = (const act_t*)a.v_new;
@@ -276,7 +283,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int p = p_first + ty + 16 * i;          // this row's position (rows beyond nq are never stored)
-      const int c0 = (p / a.block) * a.block;
+      const int c0 = first_visible(a, p);
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -317,6 +324,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
       for (int i = 0; i < 4; ++i) w[i] = sP[(ty + 16 * i) * (TK + 1) + j];
 #pragma unroll
       for (int c = 0; c < VC; ++c) {
+        if (c == VC - 1 && !vlast) break;
         const float4 v = ld4_act<act_t>(sV + j * V + tx * 4 + 32 * c);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -334,13 +342,20 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
     if (r >= nq) continue;
     const int t = t_first + r;
     float f = a.out_mult / l[i];
-    if (a.gate) f *= sigmoid_f(ld_act((const act_t*)a.gate, (size_t)t * a.ldg + h));
+    const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
+    if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
     act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
 #pragma unroll
     for (int c = 0; c < VC; ++c) {
       const int ch = tx * 4 + 32 * c;
-      st_act(o, ch + 0, acc[i][c][0] * f); st_act(o, ch + 1, acc[i][c][1] * f);
-      st_act(o, ch + 2, acc[i][c][2] * f); st_act(o, ch + 3, acc[i][c][3] * f);
+      if (c == VC - 1 && !vlast) break;
+      float gq[4] = {f, f, f, f};
+      if (a.gate && a.gate_per_channel) {
+        const float4 gv = ld4_act<act_t>(gate + (size_t)h * V + ch);      // 16-byte aligned rows of 4-channel groups: checked by the launcher
+        gq[0] *= sigmoid_f(gv.x); gq[1] *= sigmoid_f(gv.y); gq[2] *= sigmoid_f(gv.z); gq[3] *= sigmoid_f(gv.w);
+      }
+      st_act(o, ch + 0, acc[i][c][0] * gq[0]); st_act(o, ch + 1, acc[i][c][1] * gq[1]);
+      st_act(o, ch + 2, acc[i][c][2] * gq[2]); st_act(o, ch + 3, acc[i][c][3] * gq[3]);
     }
   }
 }
@@ -355,7 +370,7 @@ static DynSmemCache g_tile_smem[8];
 
 template <typename act_t, int VC>
 static int launch_tile(const b2l_seq_attn_args* a, cudaStream_t s, int cache_slot) {
-  const size_t smem = tile_smem_bytes<act_t>(a->K, 32 * VC);
+  const size_t smem = tile_smem_bytes<act_t>(a->K, a->V);
   int rc = ensure_dyn_smem(seq_block_attention_tile_kernel<act_t, VC>, smem, g_tile_smem[cache_slot]);
   if (rc) return rc;
   dim3 grid((unsigned)((a->T + TQ - 1) / TQ), (unsigned)a->heads);
@@ -363,15 +378,16 @@ static int launch_tile(const b2l_seq_attn_args* a, cudaStream_t s, int cache_slo
   return 0;
 }
 
-// ring[p % block] <- token p for the portion's tokens in the block of its last token.
+// ring[p % block] <- token p for the portion's tokens in the block of its last token (block-local) or for its last
+// `block` tokens (sliding window).
 template <typename act_t>
 __global__ void seq_ring_append_kernel(b2l_seq_attn_args a) {
   const int slot = a.meta[0], pos0 = a.meta[1];
-  const int last = pos0 + a.T - 1, c0 = (last / a.block) * a.block;
-  const int first = max(pos0, c0);
+  const int last = pos0 + a.T - 1;
+  const int first = max(pos0, a.window > 0 ? last - a.block + 1 : (last / a.block) * a.block);
   const int p = first + blockIdx.x;
   if (p > last) return;
-  const int t = p - pos0, e = p - c0;
+  const int t = p - pos0, e = p % a.block;
   const int nk = a.kv_heads * a.K, nv = a.kv_heads * a.V;
   const act_t* kn = (const act_t*)a.k_new + (size_t)t * nk;
   const act_t* vn = (const act_t*)a.v_new + (size_t)t * a.ldv;
@@ -390,6 +406,8 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   B2L_CHECK_ARG(a->q && a->k_new && a->v_new && a->cache_k && a->cache_v && a->meta && a->out, "b2l_seq_block_attention: null pointer");
   B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->kv_heads > 0 && a->K > 0 && a->V > 0 && a->block > 0, "b2l_seq_block_attention: bad size");
   B2L_CHECK_ARG(a->heads % a->kv_heads == 0, "b2l_seq_block_attention: heads %d not a multiple of kv_heads %d", a->heads, a->kv_heads);
+  B2L_CHECK_ARG(a->window >= 0 && (a->window == 0 || a->block >= a->window), "b2l_seq_block_attention: a ring of %d positions cannot serve a window of %d",
+                a->block, a->window);
   B2L_CHECK_SUPPORTED(a->V <= ATT_VMAX * 32, "b2l_seq_block_attention: value size %d above %d", a->V, ATT_VMAX * 32);
   B2L_CHECK_ARG(a->act_dtype == B2L_BF16 || a->act_dtype == B2L_F32, "b2l_seq_block_attention: act_dtype %d unsupported", a->act_dtype);
   if (a->T == 0) return 0;
@@ -403,10 +421,11 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_block_attention: key size %d too large", a->K);
   const bool al = (((uintptr_t)a->q | (uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v) % 16) == 0;
   const size_t tile_smem = a->act_dtype == B2L_BF16 ? tile_smem_bytes<__nv_bfloat16>(a->K, a->V) : tile_smem_bytes<float>(a->K, a->V);
-  const bool tile = !split && a->T >= 16 && al && (a->K * esz) % 16 == 0 && a->V % 32 == 0 && a->V <= 128 && (a->ldv * esz) % 16 == 0 &&
-                    tile_smem <= 200 * 1024;
+  const bool gate_ok = !(a->gate && a->gate_per_channel) || (((uintptr_t)a->gate % 16) == 0 && (a->ldg * esz) % 16 == 0);
+  const bool tile = !split && a->T >= 16 && al && (a->K * esz) % 16 == 0 && (a->V * esz) % 16 == 0 && a->V % 4 == 0 && a->V <= 128 &&
+                    (a->ldv * esz) % 16 == 0 && gate_ok && tile_smem <= 200 * 1024;
   if (tile) {
-    const int vc = a->V / 32;
+    const int vc = (a->V + 31) / 32;
     int rc = 0;
     if (a->act_dtype == B2L_BF16)
       rc = vc == 1 ? launch_tile<__nv_bfloat16, 1>(a, s, 0) : vc == 2 ? launch_tile<__nv_bfloat16, 2>(a, s, 1)

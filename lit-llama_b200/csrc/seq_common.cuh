@@ -20,6 +20,16 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// A gated unit from the two halves of one product: act(a) * b, or the clamped unit g = min(a, limit),
+// u = clamp(b, -limit, limit), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_pair(float a, float b, int act, float limit) {
+  if (act == B2L_SEQ_ACT_CLAMPED_SWISH) {
+    const float g = fminf(a, limit), u = fminf(fmaxf(b, -limit), limit);
+    return g * sigmoid_f(1.702f * g) * (u + 1.0f);
+  }
+  return (act == B2L_SEQ_ACT_GELU_TANH ? gelu_tanh_f(a) : (act == B2L_SEQ_ACT_SILU ? silu_f(a) : sigmoid_f(a))) * b;
+}
+
 // Calls `fn.template operator()<T>()` with the element type of act_dtype.
 #define B2L_SEQ_DISPATCH(act_dtype, ...)                                   \
   do {                                                                     \

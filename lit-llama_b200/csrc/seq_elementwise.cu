@@ -102,13 +102,11 @@ __global__ void __launch_bounds__(256) seq_norm_add_norm_reg_kernel(const act_t*
   }
 }
 
-__device__ __forceinline__ float act_of(float a, int act) {
-  return act == B2L_SEQ_ACT_GELU_TANH ? gelu_tanh_f(a) : (act == B2L_SEQ_ACT_SILU ? silu_f(a) : sigmoid_f(a));
-}
+// Moved to seq_common.cuh: gated_pair(a, b, act, limit) = act(a) * b, or the clamped unit.
 
 // 16-byte form (F and ldgu multiples of 8 elements, aligned pointers): eight bf16 or four f32 numbers per load.
 template <typename act_t>
-__global__ void seq_gated_act_vec_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act) {
+__global__ void seq_gated_act_vec_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act, float limit) {
   constexpr int PER = 16 / sizeof(act_t);
   const act_t* g = gu + (size_t)blockIdx.x * ldgu;
   act_t* o = out + (size_t)blockIdx.x * F;
@@ -120,30 +118,29 @@ __global__ void seq_gated_act_vec_kernel(const act_t* __restrict__ gu, int ldgu,
       uint32_t rw[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float lo = act_of(__uint_as_float(aw[q] << 16), act) * __uint_as_float(bw[q] << 16);
-        const float hi = act_of(__uint_as_float(aw[q] & 0xffff0000u), act) * __uint_as_float(bw[q] & 0xffff0000u);
+        const float lo = gated_pair(__uint_as_float(aw[q] << 16), __uint_as_float(bw[q] << 16), act, limit);
+        const float hi = gated_pair(__uint_as_float(aw[q] & 0xffff0000u), __uint_as_float(bw[q] & 0xffff0000u), act, limit);
         const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
         rw[q] = *reinterpret_cast<const uint32_t*>(&t);
       }
       r4 = make_uint4(rw[0], rw[1], rw[2], rw[3]);
     } else {
-      r4.x = __float_as_uint(act_of(__uint_as_float(a4.x), act) * __uint_as_float(b4.x));
-      r4.y = __float_as_uint(act_of(__uint_as_float(a4.y), act) * __uint_as_float(b4.y));
-      r4.z = __float_as_uint(act_of(__uint_as_float(a4.z), act) * __uint_as_float(b4.z));
-      r4.w = __float_as_uint(act_of(__uint_as_float(a4.w), act) * __uint_as_float(b4.w));
+      r4.x = __float_as_uint(gated_pair(__uint_as_float(a4.x), __uint_as_float(b4.x), act, limit));
+      r4.y = __float_as_uint(gated_pair(__uint_as_float(a4.y), __uint_as_float(b4.y), act, limit));
+      r4.z = __float_as_uint(gated_pair(__uint_as_float(a4.z), __uint_as_float(b4.z), act, limit));
+      r4.w = __float_as_uint(gated_pair(__uint_as_float(a4.w), __uint_as_float(b4.w), act, limit));
     }
     *reinterpret_cast<uint4*>(o + j) = r4;
   }
 }
 
 template <typename act_t>
-__global__ void seq_gated_act_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act) {
+__global__ void seq_gated_act_kernel(const act_t* __restrict__ gu, int ldgu, act_t* __restrict__ out, int F, int act, float limit) {
   const act_t* g = gu + (size_t)blockIdx.x * ldgu;
   act_t* o = out + (size_t)blockIdx.x * F;
   for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < F; j += gridDim.y * blockDim.x) {
     const float a = ld_act(g, j), b = ld_act(g, (size_t)F + j);
-    const float f = act == B2L_SEQ_ACT_GELU_TANH ? gelu_tanh_f(a) : (act == B2L_SEQ_ACT_SILU ? silu_f(a) : sigmoid_f(a));
-    st_act(o, j, f * b);
+    st_act(o, j, gated_pair(a, b, act, limit));
   }
 }
 
@@ -398,20 +395,21 @@ extern "C" int b2l_seq_norm_add_norm(const void* y, const void* w_post, float ep
   return 0;
 }
 
-extern "C" int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, int act_dtype, b2l_stream_t stream) {
+extern "C" int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, float limit, int act_dtype, b2l_stream_t stream) {
   B2L_CHECK_ARG(gu && out, "b2l_seq_gated_act: null pointer");
   B2L_CHECK_ARG(T >= 0 && F > 0 && ldgu >= 2 * F, "b2l_seq_gated_act: bad size");
-  B2L_CHECK_ARG(act >= 0 && act <= 2, "b2l_seq_gated_act: unknown activation %d", act);
+  B2L_CHECK_ARG(act >= 0 && act <= 3, "b2l_seq_gated_act: unknown activation %d", act);
+  B2L_CHECK_ARG(act != B2L_SEQ_ACT_CLAMPED_SWISH || limit > 0.f, "b2l_seq_gated_act: the clamped unit needs a positive limit");
   if (T == 0) return 0;
   const bool vec = F % 8 == 0 && ldgu % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0;
   B2L_SEQ_DISPATCH(act_dtype, {
     if (vec) {
       const int per = 16 / (int)sizeof(act_t);
       dim3 grid((unsigned)T, (unsigned)std::min((F / per + 255) / 256, 64));
-      seq_gated_act_vec_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)gu, ldgu, (act_t*)out, F, act);
+      seq_gated_act_vec_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)gu, ldgu, (act_t*)out, F, act, limit);
     } else {
       dim3 grid((unsigned)T, (unsigned)std::min((F + 255) / 256, 64));
-      seq_gated_act_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)gu, ldgu, (act_t*)out, F, act);
+      seq_gated_act_kernel<act_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const act_t*)gu, ldgu, (act_t*)out, F, act, limit);
     }
   });
   B2L_LAUNCH_CHECK("seq_gated_act_kernel");

@@ -1,5 +1,6 @@
-// Mixture-of-experts feed-forward: the router (softmax scores, a selection bias that only steers the choice, groups
-// of neighbouring experts of which only the best may be chosen, top-k, weights renormalised over the chosen), the
+// Mixture-of-experts feed-forward: the router (softmax or sigmoid scores, a selection bias that only steers the choice,
+// groups of neighbouring experts of which only the best may be chosen, top-k, weights renormalised over the chosen or
+// the scores themselves; the weight scales an expert's output or its input), the
 // expert products for a handful of tokens with the expert index read on the device (a captured single-token step
 // replays for any routing), and the sort / gather / combine around the per-expert library products of long portions.
 // Experts with index >= n_real are identities: their output is the input itself.
@@ -28,20 +29,28 @@ __device__ __forceinline__ Best warp_best(Best x) {
 // The router of one token by one warp, from its logits zr[n] (global or shared).  s[n] (scores), c[n] (choice
 // scores) and g[groups] are the warp's shared scratch.
 __device__ __forceinline__ void route_token(const float* zr, const float* __restrict__ corr, int n, int groups, int keep, int top,
-                                            int* __restrict__ idx_t, float* __restrict__ wgt_t, float* s, float* c, float* g, int lane) {
-  float mx = -INFINITY;
-  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, zr[i]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int i = lane; i < n; i += 32) {
-    const float e = expf(zr[i] - mx);
-    s[i] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  for (int i = lane; i < n; i += 32) {
-    s[i] = s[i] / sum;
-    c[i] = s[i] + (corr ? corr[i] : 0.f);
+                                            int score_fn, int renorm, int* __restrict__ idx_t, float* __restrict__ wgt_t, float* s, float* c,
+                                            float* g, int lane) {
+  if (score_fn == B2L_SEQ_SCORE_SIGMOID) {
+    for (int i = lane; i < n; i += 32) {
+      s[i] = sigmoid_f(zr[i]);
+      c[i] = s[i] + (corr ? corr[i] : 0.f);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, zr[i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float e = expf(zr[i] - mx);
+      s[i] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int i = lane; i < n; i += 32) {
+      s[i] = s[i] / sum;
+      c[i] = s[i] + (corr ? corr[i] : 0.f);
+    }
   }
   __syncwarp();
   if (groups > 1 && keep < groups) {
@@ -78,18 +87,19 @@ __device__ __forceinline__ void route_token(const float* zr, const float* __rest
     total += s[e];
     __syncwarp();
   }
-  for (int k = lane; k < top; k += 32) wgt_t[k] = s[idx_t[k]] / (total + 1e-20f);
+  for (int k = lane; k < top; k += 32) wgt_t[k] = renorm ? s[idx_t[k]] / (total + 1e-20f) : s[idx_t[k]];
 }
 
 // One warp per token.  Shared per warp: s[n], c[n], g[groups].
 __global__ void seq_moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int n, int groups, int keep,
-                                     int top, int* __restrict__ idx, float* __restrict__ wgt, int T) {
+                                     int top, int score_fn, int renorm, int* __restrict__ idx, float* __restrict__ wgt, int T) {
   extern __shared__ float route_smem[];
   const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * wpc + warp;
   if (t >= T) return;
   float* s = route_smem + (size_t)warp * (2 * n + groups);
-  route_token(z + (size_t)t * ldz, corr, n, groups, keep, top, idx + (size_t)t * top, wgt + (size_t)t * top, s, s + n, s + 2 * n, lane);
+  route_token(z + (size_t)t * ldz, corr, n, groups, keep, top, score_fn, renorm, idx + (size_t)t * top, wgt + (size_t)t * top, s, s + n, s + 2 * n,
+              lane);
 }
 
 // Dot product of a weight row with a vector in shared memory (f32); the warp's lanes stride the row.
@@ -125,7 +135,8 @@ __device__ __forceinline__ float row_dot(const act_t* __restrict__ w, const floa
 template <typename act_t>
 __global__ void __launch_bounds__(1024) seq_moe_route_fused_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wr,
                                                                   const float* __restrict__ corr, int D, int n, int groups, int keep, int top,
-                                                                  int* __restrict__ idx, float* __restrict__ wgt, int vec) {
+                                                                  int score_fn, int renorm, int* __restrict__ idx, float* __restrict__ wgt,
+                                                                  int vec) {
   extern __shared__ float route_smem[];
   float* x = route_smem;
   float* z = x + D;
@@ -137,19 +148,31 @@ __global__ void __launch_bounds__(1024) seq_moe_route_fused_kernel(const act_t* 
     if (lane == 0) z[r] = v;
   }
   __syncthreads();
-  if (warp == 0) route_token(z, corr, n, groups, keep, top, idx + (size_t)t * top, wgt + (size_t)t * top, z + n, z + 2 * n, z + 3 * n, lane);
+  if (warp == 0)
+    route_token(z, corr, n, groups, keep, top, score_fn, renorm, idx + (size_t)t * top, wgt + (size_t)t * top, z + n, z + 2 * n, z + 3 * n, lane);
 }
 
-// mid[a, j] = silu(W_gate[e] h_t . ) * (W_up[e] h_t) for assignment a = t * top + k, e = idx[a].  grid (N, ff chunks).
+// mid[a, j] = gated(W_gate[e] x, W_up[e] x) for assignment a = t * top + k, e = idx[a], x = h_t or (in_scale given) the
+// storage-type rounding of in_scale[a] * h_t.  grid (N, ff chunks).
 template <typename act_t>
 __global__ void __launch_bounds__(256) seq_moe_up_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wgu,
-                                                         const int* __restrict__ idx, act_t* __restrict__ mid, int D, int ff, int n_real,
-                                                         int top, int vec) {
+                                                         const int* __restrict__ idx, const float* __restrict__ in_scale,
+                                                         act_t* __restrict__ mid, int D, int ff, int n_real, int top, int act, float limit,
+                                                         int vec) {
   extern __shared__ float moe_x[];
   const int a = blockIdx.x, e = idx[a];
   if (e >= n_real) return;
   const act_t* hr = h + (size_t)(a / top) * ldh;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) moe_x[i] = ld_act(hr, i);
+  if (in_scale) {
+    const float w = in_scale[a];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      act_t tmp[1];
+      st_act(tmp, 0, w * ld_act(hr, i));
+      moe_x[i] = ld_act(tmp, 0);
+    }
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) moe_x[i] = ld_act(hr, i);
+  }
   __syncthreads();
   const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const act_t* w = wgu + (size_t)e * 2 * ff * D;
@@ -161,7 +184,7 @@ __global__ void __launch_bounds__(256) seq_moe_up_kernel(const act_t* __restrict
       act_t tmp[2];
       st_act(tmp, 0, gv);
       st_act(tmp, 1, uv);
-      st_act(mid, (size_t)a * ff + j, silu_f(ld_act(tmp, 0)) * ld_act(tmp, 1));
+      st_act(mid, (size_t)a * ff + j, gated_pair(ld_act(tmp, 0), ld_act(tmp, 1), act, limit));
     }
   }
 }
@@ -170,8 +193,8 @@ __global__ void __launch_bounds__(256) seq_moe_up_kernel(const act_t* __restrict
 template <typename act_t>
 __global__ void __launch_bounds__(256) seq_moe_down_kernel(const act_t* __restrict__ mid, const act_t* __restrict__ wd,
                                                            const int* __restrict__ idx, const float* __restrict__ wgt,
-                                                           const act_t* __restrict__ h, int ldh, act_t* __restrict__ y, int ldy, int D,
-                                                           int ff, int n_real, int top, int vec) {
+                                                           const float* __restrict__ in_scale, const act_t* __restrict__ h, int ldh,
+                                                           act_t* __restrict__ y, int ldy, int D, int ff, int n_real, int top, int vec) {
   extern __shared__ float moe_x[];
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) {
@@ -184,7 +207,7 @@ __global__ void __launch_bounds__(256) seq_moe_down_kernel(const act_t* __restri
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = idx[(size_t)t * top + k];
-      const float wk = wgt[(size_t)t * top + k];
+      const float wk = wgt ? wgt[(size_t)t * top + k] : 1.f;
       float v;
       if (e < n_real) {
         v = row_dot(wd + ((size_t)e * D + i) * ff, moe_x + (size_t)k * ff, ff, lane, vec);
@@ -192,7 +215,7 @@ __global__ void __launch_bounds__(256) seq_moe_down_kernel(const act_t* __restri
         st_act(tmp, 0, v);                              // an expert's output in the storage type
         v = ld_act(tmp, 0);
       } else {
-        v = ld_act(h, (size_t)t * ldh + i);
+        v = ld_act(h, (size_t)t * ldh + i) * ((wgt || in_scale == nullptr) ? 1.f : in_scale[(size_t)t * top + k]);
       }
       acc = fmaf(wk, v, acc);
     }
@@ -233,12 +256,17 @@ __global__ void seq_moe_fill_kernel(const int* __restrict__ idx, int N, int n_re
 // xg[p, :] = h[perm[p] / top, :] for p < offsets[n_real].  One CTA per row.
 template <typename act_t>
 __global__ void seq_moe_gather_kernel(const act_t* __restrict__ h, int ldh, const int* __restrict__ perm, const int* __restrict__ n_rows,
-                                      int top, act_t* __restrict__ xg, int D) {
+                                      const float* __restrict__ row_scale, int top, act_t* __restrict__ xg, int D) {
   const int p = blockIdx.x;
   if (p >= *n_rows) return;
   const act_t* src = h + (size_t)(perm[p] / top) * ldh;
   act_t* dst = xg + (size_t)p * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+  if (row_scale) {
+    const float w = row_scale[perm[p]];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) st_act(dst, i, w * ld_act(src, i));
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+  }
 }
 // y[t, i] = sum_k w[t, k] * (inv[a] >= 0 ? yg[inv[a], i] : h[t, i]).  One CTA per token.
 template <typename act_t>
@@ -250,7 +278,7 @@ __global__ void seq_moe_combine_kernel(const act_t* __restrict__ yg, const int* 
     for (int k = 0; k < top; ++k) {
       const int p = inv[(size_t)t * top + k];
       const float v = p >= 0 ? ld_act(yg, (size_t)p * D + i) : ld_act(h, (size_t)t * ldh + i);
-      acc = fmaf(wgt[(size_t)t * top + k], v, acc);
+      acc = fmaf(wgt ? wgt[(size_t)t * top + k] : 1.f, v, acc);
     }
     st_act(y, (size_t)t * ldy + i, acc);
   }
@@ -262,17 +290,19 @@ static DynSmemCache g_moe_smem[4];
 
 using namespace b2l;
 
-extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top,
-                                 int* idx, float* weights, int T, b2l_stream_t stream) {
+extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int score_fn,
+                                 int renormalize, int* idx, float* weights, int T, b2l_stream_t stream) {
   B2L_CHECK_ARG(logits && idx && weights, "b2l_seq_moe_route: null pointer");
   B2L_CHECK_ARG(T >= 0 && n > 0 && ld >= n && top > 0 && top <= n && groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups,
                 "b2l_seq_moe_route: bad size");
   B2L_CHECK_ARG((long long)keep * (n / groups) >= top, "b2l_seq_moe_route: the kept groups hold fewer than `top` experts");
+  B2L_CHECK_ARG(score_fn == B2L_SEQ_SCORE_SOFTMAX || score_fn == B2L_SEQ_SCORE_SIGMOID, "b2l_seq_moe_route: unknown score function %d", score_fn);
   if (T == 0) return 0;
   const int wpc = 4;
   const size_t smem = sizeof(float) * wpc * (2 * (size_t)n + groups);
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_moe_route: %d experts need %zu bytes of shared memory", n, smem);
-  seq_moe_route_kernel<<<(T + wpc - 1) / wpc, wpc * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, groups, keep, top, idx, weights, T);
+  seq_moe_route_kernel<<<(T + wpc - 1) / wpc, wpc * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, groups, keep, top, score_fn, renormalize, idx,
+                                                                                          weights, T);
   B2L_LAUNCH_CHECK("seq_moe_route_kernel");
   return 0;
 }
@@ -280,11 +310,13 @@ extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* corre
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups,
-                                       int keep, int top, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream) {
+                                       int keep, int top, int score_fn, int renormalize, int* idx, float* weights, int T, int act_dtype,
+                                       b2l_stream_t stream) {
   B2L_CHECK_ARG(h && w_router && idx && weights, "b2l_seq_moe_route_fused: null pointer");
   B2L_CHECK_ARG(T >= 0 && D > 0 && ldh >= D && n > 0 && top > 0 && top <= n && groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups,
                 "b2l_seq_moe_route_fused: bad size");
   B2L_CHECK_ARG((long long)keep * (n / groups) >= top, "b2l_seq_moe_route_fused: the kept groups hold fewer than `top` experts");
+  B2L_CHECK_ARG(score_fn == B2L_SEQ_SCORE_SOFTMAX || score_fn == B2L_SEQ_SCORE_SIGMOID, "b2l_seq_moe_route_fused: unknown score function %d", score_fn);
   if (T == 0) return 0;
   const size_t smem = sizeof(float) * ((size_t)D + 3 * (size_t)n + groups);
   B2L_CHECK_SUPPORTED(smem <= 200 * 1024, "b2l_seq_moe_route_fused: width %d and %d experts need %zu bytes of shared memory", D, n, smem);
@@ -295,7 +327,7 @@ extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_rou
     const int rc = ensure_dyn_smem(seq_moe_route_fused_kernel<act_t>, smem, cache[sizeof(act_t) == 2 ? 0 : 1]);
     if (rc != 0) return rc;
     seq_moe_route_fused_kernel<act_t><<<T, n >= 32 ? 1024 : 32 * ((n + 3) / 4 * 4 > 8 ? (n + 3) / 4 * 4 : 8), smem, (cudaStream_t)stream>>>((const act_t*)h, ldh, (const act_t*)w_router, correction, D, n, groups,
-                                                                             keep, top, idx, weights, vec);
+                                                                             keep, top, score_fn, renormalize, idx, weights, vec);
   });
   B2L_LAUNCH_CHECK("seq_moe_route_fused_kernel");
   return 0;
@@ -303,9 +335,10 @@ extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_rou
 
 extern "C" int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_gate_up, const void* w_down, const int* idx,
                                          const float* weights, void* mid, void* y, int ldy, int T, int D, int ff, int n_real,
-                                         int top, int act_dtype, b2l_stream_t stream) {
+                                         int top, int act, float limit, int weight_input, int act_dtype, b2l_stream_t stream) {
   B2L_CHECK_ARG(h && idx && weights && mid && y && (n_real == 0 || (w_gate_up && w_down)), "b2l_seq_moe_experts_small: null pointer");
   B2L_CHECK_ARG(T >= 0 && D > 0 && ff > 0 && top > 0 && n_real >= 0 && ldh >= D && ldy >= D, "b2l_seq_moe_experts_small: bad size");
+  B2L_CHECK_ARG(act >= 0 && act <= 3 && (act != B2L_SEQ_ACT_CLAMPED_SWISH || limit > 0.f), "b2l_seq_moe_experts_small: bad activation");
   if (T == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem_up = sizeof(float) * (size_t)D, smem_dn = sizeof(float) * (size_t)top * ff;
@@ -319,10 +352,12 @@ extern "C" int b2l_seq_moe_experts_small(const void* h, int ldh, const void* w_g
     rc = ensure_dyn_smem(seq_moe_down_kernel<act_t>, smem_dn, g_moe_smem[sizeof(act_t) == 2 ? 2 : 3]);
     if (rc != 0) return rc;
     if (n_real > 0)
-      seq_moe_up_kernel<act_t><<<dim3(T * top, (ff + 7) / 8), 256, smem_up, st>>>((const act_t*)h, ldh, (const act_t*)w_gate_up, idx, (act_t*)mid,
-                                                                                   D, ff, n_real, top, vec_up);
-    seq_moe_down_kernel<act_t><<<dim3(T, (D + 7) / 8), 256, smem_dn, st>>>((const act_t*)mid, (const act_t*)w_down, idx, weights, (const act_t*)h,
-                                                                            ldh, (act_t*)y, ldy, D, ff, n_real, top, vec_dn);
+      seq_moe_up_kernel<act_t><<<dim3(T * top, (ff + 7) / 8), 256, smem_up, st>>>((const act_t*)h, ldh, (const act_t*)w_gate_up, idx,
+                                                                                   weight_input ? weights : nullptr, (act_t*)mid, D, ff, n_real,
+                                                                                   top, act, limit, vec_up);
+    seq_moe_down_kernel<act_t><<<dim3(T, (D + 7) / 8), 256, smem_dn, st>>>((const act_t*)mid, (const act_t*)w_down, idx,
+                                                                            weight_input ? nullptr : weights, weight_input ? weights : nullptr,
+                                                                            (const act_t*)h, ldh, (act_t*)y, ldy, D, ff, n_real, top, vec_dn);
   });
   B2L_LAUNCH_CHECK("seq_moe_up_kernel / seq_moe_down_kernel");
   return 0;
@@ -341,13 +376,13 @@ extern "C" int b2l_seq_moe_sort(const int* idx, int N, int n_real, int* offsets,
   return 0;
 }
 
-extern "C" int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const int* n_rows, int top, void* xg, int N, int D,
-                                  int act_dtype, b2l_stream_t stream) {
+extern "C" int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const int* n_rows, const float* row_scale, int top, void* xg,
+                                  int N, int D, int act_dtype, b2l_stream_t stream) {
   B2L_CHECK_ARG(h && perm && n_rows && xg, "b2l_seq_moe_gather: null pointer");
   B2L_CHECK_ARG(N >= 0 && D > 0 && top > 0 && ldh >= D, "b2l_seq_moe_gather: bad size");
   if (N == 0) return 0;
   B2L_SEQ_DISPATCH(act_dtype, {
-    seq_moe_gather_kernel<act_t><<<N, 128, 0, (cudaStream_t)stream>>>((const act_t*)h, ldh, perm, n_rows, top, (act_t*)xg, D);
+    seq_moe_gather_kernel<act_t><<<N, 128, 0, (cudaStream_t)stream>>>((const act_t*)h, ldh, perm, n_rows, row_scale, top, (act_t*)xg, D);
   });
   B2L_LAUNCH_CHECK("seq_moe_gather_kernel");
   return 0;
@@ -355,7 +390,7 @@ extern "C" int b2l_seq_moe_gather(const void* h, int ldh, const int* perm, const
 
 extern "C" int b2l_seq_moe_combine(const void* yg, const int* inv, const float* weights, const void* h, int ldh, void* y, int ldy,
                                    int T, int D, int top, int act_dtype, b2l_stream_t stream) {
-  B2L_CHECK_ARG(yg && inv && weights && h && y, "b2l_seq_moe_combine: null pointer");
+  B2L_CHECK_ARG(yg && inv && h && y, "b2l_seq_moe_combine: null pointer");
   B2L_CHECK_ARG(T >= 0 && D > 0 && top > 0 && ldh >= D && ldy >= D, "b2l_seq_moe_combine: bad size");
   if (T == 0) return 0;
   B2L_SEQ_DISPATCH(act_dtype, {

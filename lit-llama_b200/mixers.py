@@ -11,7 +11,13 @@ constants are constructor parameters.
     LatentAttention      causal softmax attention whose keys and values are linear images of one cached latent per position
                          (+ one rotated key part shared by the heads), low-rank queries, a learned sink per head
     RetentionMixer       linear attention with a fixed decay per head, rotated q / k, per-head unit-RMS read-out, silu gate
-    MoEFeedForward       routed gated experts: softmax scores, selection bias, expert groups, top-k, identity experts
+    MoEFeedForward       routed gated experts: softmax or sigmoid scores, selection bias, expert groups, top-k, identity
+                         experts, weights renormalised or not, on an expert's output or on its input, clamped gated unit
+    SlidingWindowAttention  causal softmax attention over the last `window` positions: q/k norm over the whole projection
+                         or per head, partial rotation, grouped kv heads, values mixed with an earlier layer's, a sigmoid
+                         gate per output channel, ring cache of `window` positions
+    PairHashEmbedding    token embedding plus a hashed (previous token, token) embedding, into several residual streams
+    HyperConnection      one sublayer's read weights, stream-mixing matrix and write weights over several residual streams
 
 A mixer is built from a dict of weight tensors (`from_weights`) and runs one portion of one sequence:
 `forward(h, ctx)` with h [T, width] in the model's activation dtype.  Products go through torch (cuBLAS), as the
@@ -37,6 +43,7 @@ class StepContext:
                  slot_hint: Optional[int] = None) -> None:
         self.T, self.meta, self.state, self.dtype, self.pos_hint, self.slot_hint = T, meta, state, dtype, pos_hint, slot_hint
         self.act = S.act_code(dtype)
+        self.shared: Dict[str, object] = {}      # what one layer of this step hands to later ones (values of an earlier layer, ...)
 
     @property
     def stream(self) -> int:
@@ -83,13 +90,13 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------------ feed-forward
 class GatedMLP:
-    ACTS = {"gelu_tanh": S.ACT_GELU_TANH, "silu": S.ACT_SILU}
+    ACTS = {"gelu_tanh": S.ACT_GELU_TANH, "silu": S.ACT_SILU, "clamped_swish": S.ACT_CLAMPED_SWISH}
 
-    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, act: str = "gelu_tanh") -> None:
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, act: str = "gelu_tanh", limit: float = 0.0) -> None:
         self.ff = gate.shape[0]
         self.w_in = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = down.contiguous()
-        self.act = self.ACTS[act]
+        self.act, self.limit = self.ACTS[act], float(limit)
 
     def state_specs(self) -> Dict[str, StateSpec]:
         return {}
@@ -97,7 +104,8 @@ class GatedMLP:
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         gu = linear(h, self.w_in)
         mid = torch.empty((ctx.T, self.ff), dtype=h.dtype, device=h.device)
-        S.check(S.lib().b2l_seq_gated_act(_p(gu), 2 * self.ff, _p(mid), ctx.T, self.ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+        S.check(S.lib().b2l_seq_gated_act(_p(gu), 2 * self.ff, _p(mid), ctx.T, self.ff, self.act, self.limit, ctx.act, ctx.stream),
+                "b2l_seq_gated_act")
         return linear(mid, self.w_down)
 
 
@@ -356,6 +364,138 @@ class ParallelMixer:
         return linear(out, self.w_o)
 
 
+class SlidingWindowAttention:
+    """Causal softmax attention over the last `window` positions (the query's own and the window - 1 before it).
+
+        q, k, v = W_q h, W_k h, W_v h (one stacked product, with the gate);  q, k: RMS norm, over the whole projection
+        with a weight of its size (`norm_over` = "row") or per head with one weight of `dim` entries ("head"), then
+        rotation of the first rot.dims entries of every head (entry i with entry i + dims/2)
+        v <- (1 - lambda) v + lambda v_first in every layer with `v_mix` but the first of them, whose v is v_first
+        weights = softmax(q . k * scale) over the visible keys (ordinary softmax, no sink); query head h reads
+        key / value head h // (heads / kv_heads)
+        y = W_o (concat_h(sum_j weight_j v_j) * sigmoid(W_g h))            a gate per output channel
+
+    State per sequence: a ring of `window` positions of rotated keys and (mixed) values, entry position % window.  The
+    first value-mixing layer of a step leaves its values in `ctx.shared` for the later ones."""
+
+    def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, window: int,
+                 eps: float, rot: Optional[dict] = None, v_mix: bool = False, norm_over: str = "row", mix_key: str = "v_first") -> None:
+        self.name, self.H, self.G, self.K, self.V, self.scale, self.eps = name, int(heads), int(kv_heads), int(dim), int(vdim), float(scale), eps
+        self.window = int(window)
+        if self.window < 1 or self.H % self.G:
+            raise ValueError("sliding-window attention: the window must hold at least the query's own position, heads a multiple of kv_heads")
+        if norm_over not in ("row", "head"):
+            raise ValueError(f"sliding-window attention: norm over {norm_over!r}")
+        self.whole_row, self.v_mix, self.mix_key = int(norm_over == "row"), bool(v_mix), mix_key
+        assert W[p + "q"].shape[0] == heads * dim and W[p + "k"].shape[0] == kv_heads * dim and W[p + "v"].shape[0] == kv_heads * vdim, \
+            "sliding-window attention: projections do not fit the head sizes"
+        assert W[p + "g"].shape[0] == heads * vdim and W[p + "o"].shape[1] == heads * vdim, "sliding-window attention: gate / output do not fit"
+        self.w_in, (self.o_q, self.o_k, self.o_v, self.o_g) = stack_rows([W[p + "q"], W[p + "k"], W[p + "v"], W[p + "g"]])
+        self.q_norm = W[p + "q.norm"].contiguous() if (p + "q.norm") in W else None
+        self.k_norm = W[p + "k.norm"].contiguous() if (p + "k.norm") in W else None
+        self.lam = W[p + "vmix"].reshape(1).contiguous() if self.v_mix else None
+        self.w_o = W[p + "o"].contiguous()
+        self.rot_dims, self.rot_mult, self.freq = 0, 1.0, None
+        if rot and int(rot.get("dims", 0)):
+            self.rot_dims = int(rot["dims"])
+            f, self.rot_mult = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+            self.freq = f.to(self.w_o.device)
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        dt = self.w_o.dtype
+        return {self.name + ".k": StateSpec((self.window, self.G, self.K), dt, zero_on_acquire=False),
+                self.name + ".v": StateSpec((self.window, self.G, self.V), dt, zero_on_acquire=False)}
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T, dev = S.lib(), ctx.T, h.device
+        proj = linear(h, self.w_in)
+        ld = proj.shape[1]
+        q = torch.empty((T, self.H * self.K), dtype=torch.float32, device=dev)
+        kn = torch.empty((T, self.G * self.K), dtype=proj.dtype, device=dev)
+        first = ctx.shared.get(self.mix_key) if self.v_mix else None          # (tensor, column, leading dimension) of the first layer's values
+        v, v_off, ldv = proj, self.o_v, ld
+        vm = None
+        if first is not None:
+            vm = torch.empty((T, self.G * self.V), dtype=proj.dtype, device=dev)
+            v, v_off, ldv = vm, 0, self.G * self.V
+        elif self.v_mix:
+            ctx.shared[self.mix_key] = (proj, self.o_v, ld)
+        a = S.QkvPrepArgs(proj=_p(proj), ld=ld, q_off=self.o_q, k_off=self.o_k, v_off=self.o_v, q_norm=_p(self.q_norm), k_norm=_p(self.k_norm),
+                          whole_row=self.whole_row, eps=self.eps, freq=_p(self.freq), rot_dims=self.rot_dims, rot_mult=self.rot_mult,
+                          meta=_p(ctx.meta), q_out=_p(q), k_out=_p(kn), v_first=_p(first[0], first[1]) if first is not None else None,
+                          ldvf=first[2] if first is not None else 0, lambda_=_p(self.lam) if first is not None else None, v_out=_p(vm), T=T,
+                          heads=self.H, kv_heads=self.G, K=self.K, V=self.V, act_dtype=ctx.act)
+        S.check(lib.b2l_seq_qkv_prep(C.byref(a), ctx.stream), "b2l_seq_qkv_prep")
+        att = torch.empty((T, self.H * self.V), dtype=h.dtype, device=dev)
+        b = S.AttnArgs(q=_p(q), k_new=_p(kn), v_new=_p(v, v_off), ldv=ldv, cache_k=_p(ctx.state[self.name + ".k"]),
+                       cache_v=_p(ctx.state[self.name + ".v"]), meta=_p(ctx.meta), gate=_p(proj, self.o_g), ldg=ld, out=_p(att), ldo=self.H * self.V,
+                       scale=self.scale, softcap=0.0, out_mult=1.0, has_sink=0, block=self.window, T=T, heads=self.H, kv_heads=self.G, K=self.K,
+                       V=self.V, act_dtype=ctx.act, window=self.window, gate_per_channel=1)
+        S.check(lib.b2l_seq_block_attention(C.byref(b), ctx.stream), "b2l_seq_block_attention")
+        return linear(att, self.w_o)
+
+
+# ------------------------------------------------------------------------------------------------ residual streams
+class PairHashEmbedding:
+    """x = embed[token] * scale + pair[(previous token * mul_prev + token * mul_cur) mod buckets], the first token of a
+    sequence reading the pair table's last row (number `buckets`); written into `streams` equal residual streams
+    [T, streams, width] (f32).  `pair` None: the token embedding alone.  State per sequence: its last token."""
+
+    def __init__(self, name: str, embed: torch.Tensor, pair: Optional[torch.Tensor], *, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0,
+                 scale: float = 1.0, streams: int = 1) -> None:
+        self.name, self.embed, self.pair = name, embed.contiguous(), pair.contiguous() if pair is not None else None
+        self.vocab, self.width = self.embed.shape
+        self.buckets, self.mul_prev, self.mul_cur, self.scale, self.streams = int(buckets), int(mul_prev), int(mul_cur), float(scale), int(streams)
+        if self.pair is not None and tuple(self.pair.shape) != (self.buckets + 1, self.width):
+            raise ValueError(f"pair embedding is {tuple(self.pair.shape)}, {self.buckets} buckets and a first-token row need {(self.buckets + 1, self.width)}")
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {self.name + ".prev": StateSpec((1,), torch.int32)} if self.pair is not None else {}
+
+    def forward(self, tokens: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        x = torch.empty((ctx.T, self.streams, self.width), dtype=torch.float32, device=self.embed.device)
+        prev = ctx.state[self.name + ".prev"] if self.pair is not None else None
+        S.check(S.lib().b2l_seq_embed_pair(_p(tokens), int(tokens.dtype == torch.int64), _p(self.embed), _p(self.pair), self.scale, _p(prev),
+                                           _p(ctx.meta), self.mul_prev, self.mul_cur, self.buckets, _p(x), ctx.T, self.width, self.vocab,
+                                           self.streams, ctx.act, ctx.stream), "b2l_seq_embed_pair")
+        return x
+
+
+class HyperConnection:
+    """One sublayer over `streams` residual streams: it reads u = sum_s read[s] x_s, and its result y is written as
+    x_t <- sum_s mix[s, t] x_s + write[t] y for all streams at once (mix indexed [from, to]).  The weights are f32 on
+    the device; `plain(streams)` is the ordinary residual step (one stream, all weights 1).  `step()` fuses the write
+    of one sublayer with the read and the RMS norm of the next."""
+
+    def __init__(self, read: torch.Tensor, mix: torch.Tensor, write: torch.Tensor) -> None:
+        self.streams = int(read.numel())
+        if tuple(mix.shape) != (self.streams, self.streams) or write.numel() != self.streams:
+            raise ValueError(f"hyper-connection: read {tuple(read.shape)}, mix {tuple(mix.shape)}, write {tuple(write.shape)} do not fit")
+        self.read, self.mix, self.write = (t.to(torch.float32).contiguous() for t in (read, mix, write))
+
+    @classmethod
+    def plain(cls, device, streams: int = 1) -> "HyperConnection":
+        if streams != 1:
+            raise ValueError("a plain residual step has one stream")
+        one = torch.ones(1, dtype=torch.float32, device=device)
+        return cls(one, one.reshape(1, 1), one)
+
+    @staticmethod
+    def step(x: torch.Tensor, ctx: StepContext, *, y: Optional[torch.Tensor] = None, wrote: Optional["HyperConnection"] = None,
+             reads: Optional["HyperConnection"] = None, read_weights: Optional[torch.Tensor] = None, norm: Optional[torch.Tensor] = None,
+             eps: float = 0.0, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> Optional[torch.Tensor]:
+        """x [T, streams, width] f32, updated in place with sublayer `wrote`'s result y; then, with `norm`, the input of
+        the next sublayer `reads` (or any read weights, e.g. ones for the sum of the streams): act [n_rows, width]."""
+        T, n_s, D = x.shape
+        n = T if n_rows is None else n_rows
+        rw = reads.read if reads is not None else read_weights
+        h = torch.empty((n, D), dtype=ctx.dtype, device=x.device) if norm is not None else None
+        S.check(S.lib().b2l_seq_hc_step(_p(y), _p(x), _p(wrote.mix) if y is not None else None, _p(wrote.write) if y is not None else None,
+                                        _p(rw) if norm is not None else None, _p(norm), _p(h), eps, _p(rows), n, D, n_s, ctx.act, ctx.stream),
+                "b2l_seq_hc_step")
+        return h
+
+
 # ------------------------------------------------------------------------------------------------ latent attention
 class LatentAttention:
     """Causal softmax attention over a cached latent.
@@ -509,10 +649,14 @@ class RetentionMixer:
 class MoEFeedForward:
     """y = sum over the chosen experts of weight_e * expert_e(h).
 
-        s = softmax(W_router h) over all experts (f32);  choice = s + correction (steers the choice only)
-        experts form `groups` equal groups of neighbours; only experts of the `keep` groups with the largest best
-        choice score can be chosen; the `top` largest choice scores win; weight = s / (sum of the chosen s + 1e-20)
-        expert e < experts: W_down (act(W_gate h) * (W_up h));  the last `identity` outputs of the router: h itself
+        s = softmax(W_router h) over all experts, or sigmoid of each logit (`score`), f32;  choice = s + correction
+        (steers the choice only); experts form `groups` equal groups of neighbours; only experts of the `keep` groups
+        with the largest best choice score can be chosen; the `top` largest choice scores win;
+        weight = s / (sum of the chosen s + 1e-20) when `renormalize`, else s itself
+        expert e < experts: W_down unit(W_gate x, W_up x) with unit(a, b) = act(a) * b, or the clamped unit
+        min(a, limit) * sigmoid(1.702 min(a, limit)) * (clamp(b, -limit, limit) + 1) (`act` = "clamped_swish");
+        x = h and the weight scales the expert's output, or (`weight_on` = "input") x = weight * h and the outputs are
+        summed unweighted;  the last `identity` outputs of the router: h itself
 
     A few tokens (also the captured single-token step) run with the expert index read on the device; longer portions
     sort the assignments by expert and run one pair of products per expert that received tokens."""
@@ -520,15 +664,22 @@ class MoEFeedForward:
     SMALL = 4
     grouped = True        # bf16, 16-byte rows: the library's grouped product instead of one product per expert
 
+    SCORES = {"softmax": S.SCORE_SOFTMAX, "sigmoid": S.SCORE_SIGMOID}
+
     def __init__(self, W: Dict[str, torch.Tensor], p: str, *, experts: int, identity: int, top: int, groups: int, keep: int, ff: int,
-                 act: str = "silu") -> None:
+                 act: str = "silu", limit: float = 0.0, score: str = "softmax", renormalize: bool = True, weight_on: str = "output") -> None:
         self.E, self.I, self.top, self.groups, self.keep, self.ff = int(experts), int(identity), int(top), int(groups), int(keep), int(ff)
         self.n = self.E + self.I
         if self.n % self.groups or not (1 <= self.keep <= self.groups) or self.keep * (self.n // self.groups) < self.top:
             raise ValueError("routed experts: groups / keep / top do not fit the expert count")
-        self.act = GatedMLP.ACTS[act]
-        if self.act != S.ACT_SILU:
-            raise ValueError("routed experts: the device-indexed products implement silu only")
+        self.act, self.limit = GatedMLP.ACTS[act], float(limit)
+        if self.act == S.ACT_CLAMPED_SWISH and not self.limit > 0.0:
+            raise ValueError("routed experts: the clamped unit needs a positive limit")
+        if score not in self.SCORES or weight_on not in ("output", "input"):
+            raise ValueError(f"routed experts: unknown score function {score!r} or weight placement {weight_on!r}")
+        self.score, self.renorm, self.weight_input = self.SCORES[score], int(bool(renormalize)), int(weight_on == "input")
+        if self.weight_input and self.I:
+            raise ValueError("routed experts: identity experts with weights on the input are not built")
         self.w_router = W[p + "router"].contiguous()
         assert self.w_router.shape[0] == self.n, "routed experts: the router does not have experts + identity outputs"
         self.correction = W[p + "correction"].to(torch.float32).contiguous() if (p + "correction") in W else None
@@ -552,13 +703,13 @@ class MoEFeedForward:
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         if T <= self.SMALL:        # a few tokens: the logits and the routing in one launch
             S.check(lib.b2l_seq_moe_route_fused(_p(h), D, _p(self.w_router), _p(self.correction), D, self.n, self.groups, self.keep, self.top,
-                                                _p(idx), _p(wgt), T, ctx.act, ctx.stream), "b2l_seq_moe_route_fused")
+                                                self.score, self.renorm, _p(idx), _p(wgt), T, ctx.act, ctx.stream), "b2l_seq_moe_route_fused")
             self.last_idx = idx
             return idx, wgt
         # f32 logits: bf16 activations and router weights are exact in f32, the product keeps its f32 accumulator
         z = linear_f32(h, self.w_router)
-        S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, _p(idx), _p(wgt), T,
-                                      ctx.stream), "b2l_seq_moe_route")
+        S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, self.score, self.renorm,
+                                      _p(idx), _p(wgt), T, ctx.stream), "b2l_seq_moe_route")
         self.last_idx = idx
         return idx, wgt
 
@@ -570,30 +721,33 @@ class MoEFeedForward:
         if T <= self.SMALL or E == 0:
             mid = torch.empty((N, ff), dtype=h.dtype, device=dev)
             S.check(lib.b2l_seq_moe_experts_small(_p(h), D, _p(self.w_gu) if E else None, _p(self.w_down) if E else None, _p(idx), _p(wgt), _p(mid),
-                                                  _p(y), D, T, D, ff, E, top, ctx.act, ctx.stream), "b2l_seq_moe_experts_small")
+                                                  _p(y), D, T, D, ff, E, top, self.act, self.limit, self.weight_input, ctx.act, ctx.stream),
+                    "b2l_seq_moe_experts_small")
             return y
         meta = torch.empty((2 * (E + 1) + 2 * N,), dtype=torch.int32, device=dev)
         offsets, cursor, perm, inv = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:2 * E + 2 + N], meta[2 * E + 2 + N:]
         S.check(lib.b2l_seq_moe_sort(_p(idx), N, E, _p(offsets), _p(cursor), _p(perm), _p(inv), ctx.stream), "b2l_seq_moe_sort")
         xg = torch.empty((N + 8, D), dtype=h.dtype, device=dev)       # rows past the last group's end are never read
-        S.check(lib.b2l_seq_moe_gather(_p(h), D, _p(perm), _p(offsets, E), top, _p(xg), N, D, ctx.act, ctx.stream), "b2l_seq_moe_gather")
+        S.check(lib.b2l_seq_moe_gather(_p(h), D, _p(perm), _p(offsets, E), _p(wgt) if self.weight_input else None, top, _p(xg), N, D, ctx.act,
+                                       ctx.stream), "b2l_seq_moe_gather")
         gu = torch.empty((N, 2 * ff), dtype=h.dtype, device=dev)
         mid = torch.empty((N + 8, ff), dtype=h.dtype, device=dev)
         if self.grouped and h.dtype == torch.bfloat16 and D % 8 == 0 and ff % 8 == 0:
             # the library's grouped product: every expert's rows in one launch, group ends read on the device
             ends = offsets[1:]
             gu = F.grouped_mm(xg, self.w_gu.transpose(1, 2), offs=ends)
-            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), N, ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), N, ff, self.act, self.limit, ctx.act, ctx.stream), "b2l_seq_gated_act")
             yg = F.grouped_mm(mid, self.w_down.transpose(1, 2), offs=ends)
         else:
             off = offsets.cpu().tolist()                               # the one host read of a long portion
             for e in range(E):
                 if off[e + 1] > off[e]:
                     torch.mm(xg[off[e]:off[e + 1]], self.w_gu[e].t(), out=gu[off[e]:off[e + 1]])
-            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), off[E], ff, self.act, ctx.act, ctx.stream), "b2l_seq_gated_act")
+            S.check(lib.b2l_seq_gated_act(_p(gu), 2 * ff, _p(mid), off[E], ff, self.act, self.limit, ctx.act, ctx.stream), "b2l_seq_gated_act")
             yg = torch.empty((N, D), dtype=h.dtype, device=dev)
             for e in range(E):
                 if off[e + 1] > off[e]:
                     torch.mm(mid[off[e]:off[e + 1]], self.w_down[e].t(), out=yg[off[e]:off[e + 1]])
-        S.check(lib.b2l_seq_moe_combine(_p(yg), _p(inv), _p(wgt), _p(h), D, _p(y), D, T, D, top, ctx.act, ctx.stream), "b2l_seq_moe_combine")
+        S.check(lib.b2l_seq_moe_combine(_p(yg), _p(inv), None if self.weight_input else _p(wgt), _p(h), D, _p(y), D, T, D, top, ctx.act,
+                                        ctx.stream), "b2l_seq_moe_combine")
         return y

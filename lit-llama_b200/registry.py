@@ -35,6 +35,13 @@ def _load_zenasun(model_dir: str, dtype: torch.dtype, device: torch.device, max_
     return zenasun.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
 
 
+@register("Zuvevik")
+def _load_zuvevik(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
+    from . import zuvevik
+
+    return zuvevik.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
+
+
 @register("LLaMA")
 def _load_llama(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
     """config.json: {"architecture": "LLaMA", "name": "7B" | sizes..., "quantize": null | "gptq.int4" | ..., "checkpoint": file}."""

@@ -236,7 +236,7 @@ def kernel_table(model, engine, T: int, device, timer: _Timer, peaks: dict) -> L
         mlp = model.layers[0].mlp
         gu = torch.randn(tt, 2 * mlp.ff, device=device).to(dt)
         mid = torch.empty(tt, mlp.ff, dtype=dt, device=device)
-        t = timer(lambda: S.check(lib.b2l_seq_gated_act(M._p(gu), 2 * mlp.ff, M._p(mid), tt, mlp.ff, S.ACT_GELU_TANH, ctx.act, ctx.stream), "k"))
+        t = timer(lambda: S.check(lib.b2l_seq_gated_act(M._p(gu), 2 * mlp.ff, M._p(mid), tt, mlp.ff, S.ACT_GELU_TANH, 0.0, ctx.act, ctx.stream), "k"))
         add("seq_gated_act_kernel", "silu_mul_kernel", t, tt * mlp.ff * 3 * es)
         for kind, mx in by_kind.items():
             hh = torch.randn(tt, D, device=device).to(dt)

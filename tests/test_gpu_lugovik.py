@@ -508,7 +508,7 @@ def test_gated_activation_both_forms(F, dtype):
     gu = (torch.randn(T, 2 * F) * 3).to(dtype)
     mid = torch.empty(T, F, device=DEV, dtype=dtype)
     for act, fn in ((S.ACT_GELU_TANH, O.gelu_tanh), (S.ACT_SILU, O.silu)):
-        S.check(S.lib().b2l_seq_gated_act(M._p(dev(gu)), 2 * F, M._p(mid), T, F, act, ctx.act, ctx.stream), "act")
+        S.check(S.lib().b2l_seq_gated_act(M._p(dev(gu)), 2 * F, M._p(mid), T, F, act, 0.0, ctx.act, ctx.stream), "act")
         assert rel(mid, fn(gu[:, :F].double()) * gu[:, F:].double()) < (1e-6 if dtype == torch.float32 else 4e-3)
 
 
@@ -529,7 +529,7 @@ def test_row_kernels():
     assert rel(out, O.rms_norm(x2[[4, 0, 4]], w1.double(), 1e-5)) < 1e-6
     gu = torch.randn(T, 2 * 33) * 3
     mid = torch.empty(T, 33, device=DEV)
-    S.check(lib.b2l_seq_gated_act(M._p(dev(gu)), 66, M._p(mid), T, 33, S.ACT_GELU_TANH, ctx.act, ctx.stream), "act")
+    S.check(lib.b2l_seq_gated_act(M._p(dev(gu)), 66, M._p(mid), T, 33, S.ACT_GELU_TANH, 0.0, ctx.act, ctx.stream), "act")
     assert rel(mid, O.gelu_tanh(gu[:, :33].double()) * gu[:, 33:].double()) < 1e-6
     tab, tok = torch.randn(11, D), torch.tensor([3, 10, 0, 3, 7, 1])
     emb = torch.empty(T, D, device=DEV)

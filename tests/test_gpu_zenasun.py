@@ -461,7 +461,7 @@ def test_group_limit_and_negative_choice_scores():
     idx = torch.empty(T, 2, dtype=torch.int32, device=DEV)
     wgt = torch.empty(T, 2, device=DEV)
     zd, cd = z.to(DEV), corr.to(DEV)
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, cd.data_ptr(), n, 4, 3, 2, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, cd.data_ptr(), n, 4, 3, 2, S.SCORE_SOFTMAX, 1, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     s = torch.softmax(z.double(), -1)[0]
     choice = s + corr.double()
     assert float(choice[2]) < float(choice.max()) and 2 not in idx.cpu().tolist()[0]
@@ -470,7 +470,7 @@ def test_group_limit_and_negative_choice_scores():
     assert idx.cpu().tolist()[0] == best
     assert torch.allclose(wgt.cpu().double()[0], s[best] / s[best].sum(), rtol=1e-5)
     # with every group kept the same expert wins on its choice score only if the correction lets it
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 4, 4, 2, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 4, 4, 2, S.SCORE_SOFTMAX, 1, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     assert idx.cpu().tolist()[0][0] == 2
 
 
