@@ -412,14 +412,16 @@ class SlidingWindowAttention:
         ld = proj.shape[1]
         q = torch.empty((T, self.H * self.K), dtype=torch.float32, device=dev)
         kn = torch.empty((T, self.G * self.K), dtype=proj.dtype, device=dev)
-        first = ctx.shared.get(self.mix_key) if self.v_mix else None          # (tensor, column, leading dimension) of the first layer's values
+        first = ctx.shared.get(self.mix_key) if self.v_mix else None          # (tensor, column, leading dimension, width) of the first layer's values
+        if first is not None and first[3] != self.G * self.V:
+            raise ValueError(f"{self.name}: values of {self.G * self.V} entries cannot be mixed with the first layer's {first[3]}")
         v, v_off, ldv = proj, self.o_v, ld
         vm = None
         if first is not None:
             vm = torch.empty((T, self.G * self.V), dtype=proj.dtype, device=dev)
             v, v_off, ldv = vm, 0, self.G * self.V
         elif self.v_mix:
-            ctx.shared[self.mix_key] = (proj, self.o_v, ld)
+            ctx.shared[self.mix_key] = (proj, self.o_v, ld, self.G * self.V)
         a = S.QkvPrepArgs(proj=_p(proj), ld=ld, q_off=self.o_q, k_off=self.o_k, v_off=self.o_v, q_norm=_p(self.q_norm), k_norm=_p(self.k_norm),
                           whole_row=self.whole_row, eps=self.eps, freq=_p(self.freq), rot_dims=self.rot_dims, rot_mult=self.rot_mult,
                           meta=_p(ctx.meta), q_out=_p(q), k_out=_p(kn), v_first=_p(first[0], first[1]) if first is not None else None,
