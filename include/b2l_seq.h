@@ -129,8 +129,13 @@ typedef struct {
   int has_sink, block, T, heads, kv_heads, K, V, act_dtype;
   int window;                     /* 0: block-local; > 0: sliding window of that many positions */
   int gate_per_channel;           /* gate is [T, heads*V] instead of [T, heads] */
+  float* work; int work_floats;   /* optional f32 work space, see b2l_seq_block_attention_work_floats */
 } b2l_seq_attn_args;
 int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
+/* With few queries (decoding) the keys of a query are cut into chunks that run in parallel and are merged afterwards;
+ * that form needs a work space of this many floats (0: this call does not use one).  Without `work` the call runs a
+ * slower form that needs none.  The count depends on T, the head counts, V and the window or block, not on positions. */
+long long b2l_seq_block_attention_work_floats(const b2l_seq_attn_args* a);
 
 /* out[t, j] = (float) in[t, j]: act columns of a product as f32 operands of a recurrence. */
 int b2l_seq_cast_f32(const void* in, int ldin, float* out, int ldout, int T, int n, int act_dtype, b2l_stream_t stream);

@@ -45,6 +45,7 @@ class AttnArgs(C.Structure):
         ("has_sink", c_int), ("block", c_int), ("T", c_int), ("heads", c_int), ("kv_heads", c_int), ("K", c_int), ("V", c_int),
         ("act_dtype", c_int),
         ("window", c_int), ("gate_per_channel", c_int),
+        ("work", c_void_p), ("work_floats", c_int),
     ]
 
 
@@ -95,6 +96,7 @@ _SIGS = {
     "b2l_seq_headnorm_rope": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_int, c_void_p]),
     "b2l_seq_block_attention": (c_int, [C.POINTER(AttnArgs), c_void_p]),
+    "b2l_seq_block_attention_work_floats": (C.c_longlong, [C.POINTER(AttnArgs)]),
     "b2l_seq_cast_f32": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_zero_slot": (c_int, [c_void_p, c_size_t, c_int, c_void_p]),
     "b2l_seq_add_norm2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,

@@ -155,6 +155,181 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
   }
 }
 
+// ---- a few queries (decoding): a CTA takes DEC_CK consecutive keys of one query for ALL query heads of one key/value
+// group, so a cached row is read once per group: keys and values of the chunk arrive in shared memory by 16-byte
+// asynchronous copies (plain loads for odd sizes), the scores of (head, key) pairs are spread over the threads with padded
+// key rows (conflict-free 16-byte reads), a warp per head forms the chunk's softmax, and the value product gives one
+// output channel of one head per thread.  Every chunk writes {max, sum, weighted values} to the work space and a second
+// kernel merges the chunks of a (query, head), adds the sink, applies the gate and stores.  The grid covers the most keys
+// a query can see (the window or the block), not the position, so a captured single-token step replays anywhere.
+constexpr int DEC_CK = 64, DEC_THREADS = 128;
+
+__device__ __forceinline__ void dec_cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dec_cp_wait_all() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <typename act_t>
+__global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_seq_attn_args a, int n_chunks, int vec) {
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  constexpr int PER = 16 / (int)sizeof(act_t);
+  const int K = a.K, V = a.V, Kpa = K + PER, hpg = a.heads / a.kv_heads;
+  const int Vp = (V + PER - 1) / PER * PER;
+  act_t* sK = reinterpret_cast<act_t*>(dec_smem);                 // [DEC_CK][Kpa]
+  act_t* sV = sK + DEC_CK * Kpa;                                  // [DEC_CK][Vp]
+  float* sQ = reinterpret_cast<float*>(sV + DEC_CK * Vp);         // [hpg][K]
+  float* sS = sQ + hpg * K;                                       // [hpg][DEC_CK]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int slot = a.meta[0], pos0 = a.meta[1];
+  const int p = pos0 + t, lo = first_visible(a, p) + c * DEC_CK;
+  const int nv = min(DEC_CK, p - lo + 1);                         // keys of this chunk that the query sees
+  float* part = a.work + ((size_t)(t * a.heads + g * hpg) * n_chunks + c) * (V + 2);      // head hq: + hq * n_chunks * (V + 2)
+  if (nv <= 0) {
+    for (int hq = tid; hq < hpg; hq += DEC_THREADS) {
+      part[(size_t)hq * n_chunks * (V + 2)] = -INFINITY;
+      part[(size_t)hq * n_chunks * (V + 2) + 1] = 0.f;
+    }
+    return;
+  }
+  const act_t* kn = (const act_t*)a.k_new;
+  const act_t* vn = (const act_t*)a.v_new;
+  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
+  const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
+  if (vec) {
+    const int kc = K / PER, vc = V / PER;
+    for (int i = tid; i < nv * kc; i += DEC_THREADS) {
+      const int r = i / kc, e = (i - r * kc) * PER, j = lo + r;
+      dec_cp_async16(sK + r * Kpa + e, j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + e : ck + ((size_t)(j % a.block) * a.kv_heads + g) * K + e);
+    }
+    for (int i = tid; i < nv * vc; i += DEC_THREADS) {
+      const int r = i / vc, e = (i - r * vc) * PER, j = lo + r;
+      dec_cp_async16(sV + r * Vp + e, j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + e : cv + ((size_t)(j % a.block) * a.kv_heads + g) * V + e);
+    }
+  } else {
+    for (int i = tid; i < nv * K; i += DEC_THREADS) {
+      const int r = i / K, e = i - r * K, j = lo + r;
+      sK[r * Kpa + e] = j >= pos0 ? kn[((size_t)(j - pos0) * a.kv_heads + g) * K + e] : ck[((size_t)(j % a.block) * a.kv_heads + g) * K + e];
+    }
+    for (int i = tid; i < nv * V; i += DEC_THREADS) {
+      const int r = i / V, e = i - r * V, j = lo + r;
+      sV[r * Vp + e] = j >= pos0 ? vn[(size_t)(j - pos0) * a.ldv + (size_t)g * V + e] : cv[((size_t)(j % a.block) * a.kv_heads + g) * V + e];
+    }
+  }
+  for (int i = tid; i < hpg * K; i += DEC_THREADS) sQ[i] = a.q[((size_t)t * a.heads + (size_t)g * hpg) * K + i];
+  dec_cp_wait_all();
+  __syncthreads();
+  for (int i = tid; i < hpg * DEC_CK; i += DEC_THREADS) {          // a warp: 32 consecutive keys of one head
+    const int hq = i / DEC_CK, r = i - hq * DEC_CK;
+    float sc = -INFINITY;
+    if (r < nv) {
+      sc = dot_row<act_t>(sQ + hq * K, sK + r * Kpa, K, vec != 0) * a.scale;
+      if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+    }
+    sS[i] = sc;
+  }
+  __syncthreads();
+  for (int hq = warp; hq < hpg; hq += DEC_THREADS / 32) {
+    float* row = sS + hq * DEC_CK;
+    float m = -INFINITY;
+    for (int r = lane; r < DEC_CK; r += 32) m = fmaxf(m, row[r]);
+    m = warp_max(m);                                             // finite: the chunk has at least one visible key
+    float l = 0.f;
+    for (int r = lane; r < DEC_CK; r += 32) {
+      const float w = r < nv ? expf(row[r] - m) : 0.f;
+      row[r] = w;
+      l += w;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      part[(size_t)hq * n_chunks * (V + 2)] = m;
+      part[(size_t)hq * n_chunks * (V + 2) + 1] = l;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < hpg * V; i += DEC_THREADS) {
+    const int hq = i / V, ch = i - hq * V;
+    const float* w = sS + hq * DEC_CK;
+    float acc0 = 0.f, acc1 = 0.f;
+    int r = 0;
+    for (; r + 1 < nv; r += 2) {
+      acc0 = fmaf(w[r], ld_act(sV, (size_t)r * Vp + ch), acc0);
+      acc1 = fmaf(w[r + 1], ld_act(sV, (size_t)(r + 1) * Vp + ch), acc1);
+    }
+    if (r < nv) acc0 = fmaf(w[r], ld_act(sV, (size_t)r * Vp + ch), acc0);
+    part[(size_t)hq * n_chunks * (V + 2) + 2 + ch] = acc0 + acc1;
+  }
+}
+
+// out[t, h] = gate * out_mult * sum_c e^(m_c - M) acc_c / (sink e^(-M) + sum_c e^(m_c - M) l_c): one CTA per (query, head).
+// The chunk factors go through shared memory, so the loads of the channel sums do not wait for one another.
+constexpr int MERGE_THREADS = 128;
+template <typename act_t>
+__global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_seq_attn_args a, int n_chunks) {
+  extern __shared__ float merge_f[];                 // [n_chunks]
+  __shared__ float red[MERGE_THREADS / 32];
+  const int pair = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t = pair / a.heads, h = pair - t * a.heads, V = a.V;
+  const float* part = a.work + (size_t)pair * n_chunks * (V + 2);
+  float M = a.has_sink ? 0.f : -INFINITY;
+  for (int c = tid; c < n_chunks; c += MERGE_THREADS) M = fmaxf(M, part[(size_t)c * (V + 2)]);
+  M = warp_max(M);
+  if (lane == 0) red[warp] = M;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, red[w]);
+  __syncthreads();
+  float l = 0.f;
+  for (int c = tid; c < n_chunks; c += MERGE_THREADS) {
+    const float m = part[(size_t)c * (V + 2)];
+    const float f = m == -INFINITY ? 0.f : expf(m - M);
+    merge_f[c] = f;
+    if (f != 0.f) l += part[(size_t)c * (V + 2) + 1] * f;
+  }
+  l = warp_sum(l);
+  if (lane == 0) red[warp] = l;
+  __syncthreads();
+  l = 0.f;
+#pragma unroll
+  for (int w = 0; w < MERGE_THREADS / 32; ++w) l += red[w];
+  if (a.has_sink) l += expf(0.f - M);
+  float f = a.out_mult / l;
+  const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
+  if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
+  act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
+  for (int ch = tid; ch < V; ch += MERGE_THREADS) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int c = 0;
+    for (; c + 4 <= n_chunks; c += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float fc = merge_f[c + u];
+        const float v = fc != 0.f ? part[(size_t)(c + u) * (V + 2) + 2 + ch] : 0.f;      // an empty chunk wrote nothing there
+        acc[u] = fmaf(v, fc, acc[u]);
+      }
+    }
+    for (; c < n_chunks; ++c) {
+      const float fc = merge_f[c];
+      if (fc != 0.f) acc[0] = fmaf(part[(size_t)c * (V + 2) + 2 + ch], fc, acc[0]);
+    }
+    const float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    st_act(o, ch, sum * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
+  }
+}
+
+template <typename act_t>
+static size_t chunk_smem_bytes(const b2l_seq_attn_args* a) {
+  const int per = 16 / (int)sizeof(act_t), hpg = a->heads / a->kv_heads;
+  const int Vp = (a->V + per - 1) / per * per;
+  return sizeof(act_t) * ((size_t)DEC_CK * (a->K + per) + (size_t)DEC_CK * Vp) + sizeof(float) * ((size_t)hpg * a->K + (size_t)hpg * DEC_CK);
+}
+static int chunk_count(const b2l_seq_attn_args* a) { return ((a->window > 0 ? a->window : a->block) + DEC_CK - 1) / DEC_CK; }
+static bool few_queries(const b2l_seq_attn_args* a) { return a->T * a->heads < 2 * sm_count(); }
+static DynSmemCache g_chunk_smem[2];
+
 // ---- prompt portions: a CTA computes TQ queries of one head against key tiles of TK positions, SGEMM style.
 // Scores: thread (ty, tx) holds queries ty + 16 i and keys tx + 8 j (4 x 4) with q and k rows read as float4 from
 // padded shared memory; the 8 lanes of a ty group share their rows' maxima and sums by shuffles; the weights go
@@ -416,7 +591,34 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   const int vec = ((a->K * esz) % 16 == 0) && (((uintptr_t)a->k_new | (uintptr_t)a->cache_k) % 16 == 0) && (a->K % 8 == 0 || esz == 4);
   const int pairs = a->T * a->heads;
   const int Kpad = (a->K + 3) & ~3;
-  const bool split = pairs < 2 * sm_count();          // few queries (decoding): sixteen warps share one query's keys
+  const bool split = few_queries(a);                  // few queries (decoding)
+  const size_t chunk_smem = a->act_dtype == B2L_BF16 ? chunk_smem_bytes<__nv_bfloat16>(a) : chunk_smem_bytes<float>(a);
+  if (split && a->work != nullptr && chunk_smem <= 200 * 1024 && chunk_count(a) <= 8192) {     // chunks of keys in parallel, then a merge
+    const int n_chunks = chunk_count(a);
+    B2L_CHECK_ARG((size_t)a->work_floats >= (size_t)pairs * n_chunks * (a->V + 2), "b2l_seq_block_attention: work space of %d floats, %zu needed",
+                  a->work_floats, (size_t)pairs * n_chunks * (a->V + 2));
+    const int per = 16 / (int)esz;
+    const int vec16 = (a->K % per == 0 && a->V % per == 0 && a->ldv % per == 0 &&
+                       (((uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v | (uintptr_t)a->q) % 16) == 0) ? 1 : 0;
+    dim3 grid((unsigned)n_chunks, (unsigned)a->kv_heads, (unsigned)a->T);
+    if (a->act_dtype == B2L_BF16) {
+      int rc = ensure_dyn_smem(seq_attention_chunk_kernel<__nv_bfloat16>, chunk_smem, g_chunk_smem[0]);
+      if (rc) return rc;
+      seq_attention_chunk_kernel<__nv_bfloat16><<<grid, DEC_THREADS, chunk_smem, s>>>(*a, n_chunks, vec16);
+      seq_attention_merge_kernel<__nv_bfloat16><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+    } else {
+      int rc = ensure_dyn_smem(seq_attention_chunk_kernel<float>, chunk_smem, g_chunk_smem[1]);
+      if (rc) return rc;
+      seq_attention_chunk_kernel<float><<<grid, DEC_THREADS, chunk_smem, s>>>(*a, n_chunks, vec16);
+      seq_attention_merge_kernel<float><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+    }
+    B2L_LAUNCH_CHECK("seq_attention_chunk_kernel");
+    const int n_app0 = std::min(a->T, a->block);
+    if (a->act_dtype == B2L_BF16) seq_ring_append_kernel<__nv_bfloat16><<<n_app0, 128, 0, s>>>(*a);
+    else seq_ring_append_kernel<float><<<n_app0, 128, 0, s>>>(*a);
+    B2L_LAUNCH_CHECK("seq_ring_append_kernel");
+    return 0;
+  }
   const size_t smem = sizeof(float) * ((size_t)(split ? 1 : 4) * Kpad + (split ? 16 : 4) * (2 + ATT_VMAX * 32));
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_block_attention: key size %d too large", a->K);
   const bool al = (((uintptr_t)a->q | (uintptr_t)a->k_new | (uintptr_t)a->v_new | (uintptr_t)a->cache_k | (uintptr_t)a->cache_v) % 16) == 0;
@@ -447,4 +649,10 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   else seq_ring_append_kernel<float><<<n_app, 128, 0, s>>>(*a);
   B2L_LAUNCH_CHECK("seq_ring_append_kernel");
   return 0;
+}
+
+extern "C" long long b2l_seq_block_attention_work_floats(const b2l_seq_attn_args* a) {
+  if (a == nullptr || a->T <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->V <= 0 || a->block <= 0) return 0;
+  if (!few_queries(a)) return 0;
+  return (long long)a->T * a->heads * chunk_count(a) * (a->V + 2);
 }

@@ -241,6 +241,17 @@ def rope_frequencies(dims: int, base: float, scaling: Optional[dict]) -> Tuple[t
 
 
 # ------------------------------------------------------------------------------------------------ attention
+def local_attention(a: "S.AttnArgs", ctx: StepContext) -> None:
+    """b2l_seq_block_attention with the work space its few-query form asks for."""
+    lib = S.lib()
+    n = lib.b2l_seq_block_attention_work_floats(C.byref(a))
+    work = None
+    if n:
+        work = torch.empty((n,), dtype=torch.float32, device=ctx.meta.device)
+        a.work, a.work_floats = _p(work), n
+    S.check(lib.b2l_seq_block_attention(C.byref(a), ctx.stream), "b2l_seq_block_attention")
+
+
 class BlockSinkAttention:
     """Softmax attention inside blocks of `block` positions (query p sees j <= p with j // block == p // block; block
     None: the whole sequence up to `max_positions`), weights exp(s_j) / (1 + sum exp(s_j)) when `sink`.  As a branch of
@@ -289,7 +300,7 @@ class BlockSinkAttention:
                        cache_v=_p(ctx.state[self.name + ".v"]), meta=_p(ctx.meta), gate=_p(proj, o_g), ldg=ld, out=_p(out, out_off),
                        ldo=out.shape[1], scale=self.scale, softcap=self.softcap, out_mult=float(out_mult), has_sink=int(self.sink),
                        block=self.block, T=T, heads=self.H, kv_heads=self.G, K=self.K, V=self.V, act_dtype=ctx.act)
-        S.check(lib.b2l_seq_block_attention(C.byref(a), ctx.stream), "b2l_seq_block_attention")
+        local_attention(a, ctx)
 
 
 class GatedLinearAttention:
@@ -433,7 +444,7 @@ class SlidingWindowAttention:
                        cache_v=_p(ctx.state[self.name + ".v"]), meta=_p(ctx.meta), gate=_p(proj, self.o_g), ldg=ld, out=_p(att), ldo=self.H * self.V,
                        scale=self.scale, softcap=0.0, out_mult=1.0, has_sink=0, block=self.window, T=T, heads=self.H, kv_heads=self.G, K=self.K,
                        V=self.V, act_dtype=ctx.act, window=self.window, gate_per_channel=1)
-        S.check(lib.b2l_seq_block_attention(C.byref(b), ctx.stream), "b2l_seq_block_attention")
+        local_attention(b, ctx)
         return linear(att, self.w_o)
 
 

@@ -307,8 +307,9 @@ def test_registry_loads_a_saved_model(tmp_path):
         model = P.load_model(str(tmp_path), dtype=dtype, device=DEV, max_positions=64)
         assert type(model).__name__ == "Zuvevik"
         assert rel(run_whole(P.Engine(model, n_slots=1), toks), want) < tol
-    long = tokens_of(cfg, 150)                       # a ring per layer: no position limit, whatever max_positions said
-    assert rel(run_whole(P.Engine(model, n_slots=1), long), O.model(long, cfg, W)) < 0.1
+        if dtype == torch.float32:                   # a ring per layer: no position limit, whatever max_positions said
+            long = tokens_of(cfg, 150)
+            assert rel(run_whole(P.Engine(model, n_slots=1), long), O.model(long, cfg, W)) < 2e-5
 
 
 # ----------------------------------------------------------------------------- mechanisms alone
@@ -406,9 +407,10 @@ def test_attention_operands_alone(per_head):
     assert rel(qo, q.reshape(T, -1)) < 2e-6 and rel(ko, k.reshape(T, -1)) < 2e-6 and rel(vo, want_v) < 1e-6
 
 
-def _window_attention(S, q, k, v, cache_k, cache_v, gate, pos0, window, ring, scale, dtype, slot=0):
+def _window_attention(S, q, k, v, cache_k, cache_v, gate, pos0, window, ring, scale, dtype, slot=0, work=True):
     """The attention kernel on operands made by the test: q [T, H, K] f32, k [T, G, K], v [T, G, V], caches
-    [slots, ring, G, K or V], gate [T, H*V]; returns [T, H*V] and appends to the ring."""
+    [slots, ring, G, K or V], gate [T, H*V]; returns [T, H*V] and appends to the ring.  `work`: give the call the work
+    space it asks for (few queries then run as parallel key chunks with a merge), else it runs its form without one."""
     T, H, K = q.shape
     G, V = k.shape[1], v.shape[2]
     out = torch.empty(T, H * V, dtype=dtype, device=DEV)
@@ -417,6 +419,10 @@ def _window_attention(S, q, k, v, cache_k, cache_v, gate, pos0, window, ring, sc
     a = S.AttnArgs(q=qd.data_ptr(), k_new=kd.data_ptr(), v_new=vd.data_ptr(), ldv=G * V, cache_k=cache_k.data_ptr(), cache_v=cache_v.data_ptr(),
                    meta=meta.data_ptr(), gate=gd.data_ptr(), ldg=H * V, out=out.data_ptr(), ldo=H * V, scale=scale, softcap=0.0, out_mult=1.0,
                    has_sink=0, block=ring, T=T, heads=H, kv_heads=G, K=K, V=V, act_dtype=S.act_code(dtype), window=window, gate_per_channel=1)
+    n = S.lib().b2l_seq_block_attention_work_floats(C.byref(a)) if work else 0
+    buf = torch.full((max(n, 1),), float("nan"), device=DEV)
+    if n:
+        a.work, a.work_floats = buf.data_ptr(), n
     S.check(S.lib().b2l_seq_block_attention(C.byref(a), None), "attention")
     torch.cuda.synchronize()
     return out
@@ -434,19 +440,20 @@ def test_sliding_window_attention_alone(shape):
     gate = torch.randn(T, H * V, generator=g).bfloat16().float()
     want = O.windowed_softmax_attention(q.double(), k.double(), v.double(), scale, window) * torch.sigmoid(gate.double())
     for dtype, tol in ((torch.float32, 3e-6), (torch.bfloat16, 6e-3)):
-        for slot, cuts in ((0, [T]), (1, [130, 1, 2, 64, 17, 119]), (0, [200] + [1] * 133)):
+        for slot, cuts, work in ((0, [T], True), (1, [130, 1, 2, 64, 17, 119], True), (0, [200] + [1] * 133, True), (1, [150, 3, 20] + [1] * 160, False)):
             ck = torch.full((2, ring, G, K), float("nan"), dtype=dtype, device=DEV)      # stale entries must never be read
             cv = torch.full((2, ring, G, V), float("nan"), dtype=dtype, device=DEV)
             outs, at = [], 0
             for n in cuts:
-                outs.append(_window_attention(S, q[at:at + n], k[at:at + n], v[at:at + n], ck, cv, gate[at:at + n], at, window, ring, scale, dtype, slot))
+                outs.append(_window_attention(S, q[at:at + n], k[at:at + n], v[at:at + n], ck, cv, gate[at:at + n], at, window, ring, scale, dtype, slot,
+                                              work=work))
                 at += n
             assert rel(torch.cat(outs), want) < tol, (shape, dtype, cuts[:3], rel(torch.cat(outs), want))
 
 
-@pytest.mark.parametrize("V", [8, 6])
-@pytest.mark.parametrize("window", [1, 2, 31, 32, 33, 64, 65, 72])
-def test_a_dominant_key_just_inside_and_just_outside_the_window(window, V):
+@pytest.mark.parametrize("V,work", [(8, True), (6, True), (8, False)])
+@pytest.mark.parametrize("window", [1, 2, 31, 32, 33, 63, 64, 65, 72, 128, 129])
+def test_a_dominant_key_just_inside_and_just_outside_the_window(window, V, work):
     """One key is made to stand out (long, along every query); its value is a marker.  A query sees the marker exactly
     when 0 <= distance < window: in one portion (both kernels), across a portion border, and when decoding from the ring."""
     P, S, M = _pkg()
@@ -471,7 +478,8 @@ def test_a_dominant_key_just_inside_and_just_outside_the_window(window, V):
                 n = min(n, T - at)
                 if n <= 0:
                     continue
-                outs.append(_window_attention(S, q[at:at + n], k[at:at + n], v[at:at + n], ck, cv, gate[at:at + n], at, window, ring, 1.0, torch.float32))
+                outs.append(_window_attention(S, q[at:at + n], k[at:at + n], v[at:at + n], ck, cv, gate[at:at + n], at, window, ring, 1.0, torch.float32,
+                                              work=work))
                 at += n
             out = torch.cat(outs).cpu()
             for i in checks:
