@@ -99,6 +99,13 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
         h1 = torch.empty(tt, D, dtype=dt, device=device)
         t = timer(lambda: S.check(lib.b2l_seq_norm_add_norm(M._p(y), M._p(w), eps, M._p(x1), M._p(w), M._p(h1), tt, D, ctx.act, ctx.stream), "k"))
         add("  like: seq_norm_add_norm_kernel (one stream: post-norm + add + norm)", tt, t, tt * D * (es + 4 + 4 + es))
+        # ---- embedding: the token row plus the hashed pair row into every stream, against the plain embedding
+        emb = model.embedding
+        tk = torch.randint(0, emb.vocab, (tt,), device=device)
+        t = timer(lambda: emb.forward(tk, ctx))
+        add(f"seq_embed_pair_kernel (token + pair rows into {n_s} streams)", tt, t, tt * D * (2 * es + 4 * n_s))
+        t = timer(lambda: S.check(lib.b2l_seq_embed(M._p(tk), 1, M._p(emb.embed), ctx.act, 1.0, M._p(x1), tt, D, emb.vocab, ctx.stream), "k"))
+        add("  like: seq_embed_kernel (token row into one stream)", tt, t, tt * D * (es + 4))
         # ---- attention operands
         proj = torch.randn(tt, att.w_in.shape[0], device=device).to(dt)
         ld = proj.shape[1]
@@ -138,7 +145,7 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
             b = S.AttnArgs(q=M._p(qr), k_new=M._p(kr), v_new=M._p(vm), ldv=G * V, cache_k=M._p(ck), cache_v=M._p(cv), meta=M._p(meta), gate=gate,
                            ldg=ldg, out=M._p(out), ldo=H * V, scale=att.scale, softcap=0.0, out_mult=1.0, has_sink=sink, block=Wn, T=tt, heads=H,
                            kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=window, gate_per_channel=per_channel)
-            t = timer(lambda: S.check(lib.b2l_seq_block_attention(C.byref(b), ctx.stream), "k"))
+            t = timer(lambda: M.local_attention(b, ctx))
             nb = tt * (H * K * 4 + G * (K + V) * es * 2 + H * V * es * (2 if per_channel else 1)) + (kq * G * (K + V) * es if tt == 1 else 0)
             add(name, tt, t, nb, 2.0 * tt * H * kq * (K + V), f"f32 scores on CUDA cores, {kq:.0f} keys per query")
         t = timer(lambda: att.forward(hh, ctx))
