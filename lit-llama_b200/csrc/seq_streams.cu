@@ -6,7 +6,7 @@
 
 namespace b2l {
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 16;
 
 // x[t, s, :] = table[token[t]] * scale + pair[row(t)] for every stream s, with
 //   row(t) = (previous token * mul_prev + token[t] * mul_cur) mod buckets, and row `buckets` at position 0.
@@ -241,12 +241,12 @@ extern "C" int b2l_seq_hc_step(const void* y, float* X, const float* mix, const 
   if (n_rows == 0 || (y == nullptr && w_next == nullptr)) return 0;
   const size_t smem = w_next ? sizeof(float) * (size_t)D : 0;
   B2L_CHECK_SUPPORTED(smem <= 200 * 1024, "b2l_seq_hc_step: width %d too large", D);
-  static DynSmemCache cache[2 * 5];
+  static DynSmemCache cache[2 * 9];
   cudaStream_t s_ = (cudaStream_t)stream;
 #define B2L_HC_ARGS (const act_t*)y, X, mix, out_w, in_next, (const act_t*)w_next, (act_t*)h, eps, rows, D, streams
 #define B2L_HC_LAUNCH(SV, slot)                                                                                   \
   do {                                                                                                            \
-    const int rc_ = ensure_dyn_smem(seq_hc_step_kernel<act_t, SV>, smem, cache[(sizeof(act_t) == 2 ? 0 : 5) + slot]); \
+    const int rc_ = ensure_dyn_smem(seq_hc_step_kernel<act_t, SV>, smem, cache[(sizeof(act_t) == 2 ? 0 : 9) + slot]); \
     if (rc_ != 0) return rc_;                                                                                     \
     seq_hc_step_kernel<act_t, SV><<<n_rows, 256, smem, s_>>>(B2L_HC_ARGS);                                         \
   } while (0)
@@ -256,7 +256,11 @@ extern "C" int b2l_seq_hc_step(const void* y, float* X, const float* mix, const 
       case 2: B2L_HC_LAUNCH(2, 1); break;
       case 3: B2L_HC_LAUNCH(3, 2); break;
       case 4: B2L_HC_LAUNCH(4, 3); break;
-      default: B2L_HC_LAUNCH(0, 4); break;
+      case 5: B2L_HC_LAUNCH(5, 4); break;
+      case 6: B2L_HC_LAUNCH(6, 5); break;
+      case 7: B2L_HC_LAUNCH(7, 6); break;
+      case 8: B2L_HC_LAUNCH(8, 7); break;
+      default: B2L_HC_LAUNCH(0, 8); break;     // more streams: loops with run-time bounds
     }
   });
 #undef B2L_HC_LAUNCH

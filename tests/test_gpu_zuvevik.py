@@ -345,7 +345,7 @@ def test_pair_embedding_alone():
     assert float((plain.forward(torch.tensor(toks, device=DEV), ctx)[:, 0].cpu() - emb[torch.tensor(toks)]).abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("streams", [1, 2, 3, 4, 6])
+@pytest.mark.parametrize("streams", [1, 2, 3, 4, 6, 11])
 def test_hyper_connection_step_alone(streams):
     P, S, M = _pkg()
     T, D, eps = 9, 200, 1e-5
