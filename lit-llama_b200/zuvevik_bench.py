@@ -35,7 +35,7 @@ def zuvevik_config(width, layers, heads, kv_heads, dim, vdim, window, streams, f
     dense = {"kind": "dense", "ff": ff}
     routed = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
     return {"architecture": "Zuvevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": streams, "logit_scale": 1.0,
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 40503, "mul_cur": 2654435}},
             "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i == 0 else routed} for i in range(layers)]}
 
 

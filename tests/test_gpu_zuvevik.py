@@ -58,7 +58,7 @@ def cfg_b():
             "embedding": {"bigram": {"buckets": 64, "mul_prev": 1, "mul_cur": 1}},
             "layers": [
                 {"type": "attention", "mixer": attn(4, 1, 16, 16, 33, 0.25, 8), "mlp": moe(4, 1, 24, 2.5)},
-                {"type": "attention", "mixer": attn(2, 2, 32, 8, 64, 0.18, 0), "mlp": moe(7, 4, 16, 1.5)},
+                {"type": "attention", "mixer": attn(2, 2, 32, 8, 64, 0.18, 0), "mlp": moe(7, 4, 16, 1.75)},
                 {"type": "attention", "mixer": attn(4, 1, 16, 16, 17, 0.25, 16), "mlp": {"kind": "dense", "ff": 96}},
             ]}
 
@@ -325,10 +325,10 @@ def test_pair_embedding_alone():
     g = torch.Generator().manual_seed(0)
     emb, pair = torch.randn(V, D, generator=g).bfloat16().float(), torch.randn(buckets + 1, D, generator=g).bfloat16().float()
     toks = torch.randint(0, V, (40,), generator=g).tolist()
-    cfg = {"embedding": {"bigram": {"buckets": buckets, "mul_prev": 31, "mul_cur": 17}}}
+    cfg = {"embedding": {"bigram": {"buckets": buckets, "mul_prev": 29, "mul_cur": 13}}}
     want = O.embedding(toks, {"embed": emb, "bigram": pair}, cfg)
     for dtype in (torch.float32, torch.bfloat16):
-        e = M.PairHashEmbedding("pe", emb.to(DEV, dtype), pair.to(DEV, dtype), buckets=buckets, mul_prev=31, mul_cur=17, streams=3)
+        e = M.PairHashEmbedding("pe", emb.to(DEV, dtype), pair.to(DEV, dtype), buckets=buckets, mul_prev=29, mul_cur=13, streams=3)
         pool = None
         for slot, cuts in ((1, [40]), (0, [1, 1, 5, 2, 31]), (1, [13, 27])):       # slot 1 is used twice: the stale last token must not be read
             outs, at = [], 0
@@ -428,7 +428,7 @@ def _window_attention(S, q, k, v, cache_k, cache_v, gate, pos0, window, ring, sc
     return out
 
 
-@pytest.mark.parametrize("shape", [(4, 2, 16, 24, 40, 40), (8, 2, 32, 48, 70, 70), (3, 1, 10, 6, 5, 8), (8, 8, 64, 64, 33, 64), (2, 1, 20, 128, 100, 100)])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 24, 40, 40), (6, 2, 32, 56, 70, 70), (3, 1, 10, 6, 5, 8), (8, 8, 64, 64, 33, 64), (2, 1, 20, 128, 100, 100)])
 def test_sliding_window_attention_alone(shape):
     """Both attention kernels (a warp per query and head; 64-query tiles) against the oracle: whole, in portions whose
     windows reach into the ring, and token by token, in f32 and bf16; the ring may be larger than the window."""
@@ -452,7 +452,7 @@ def test_sliding_window_attention_alone(shape):
 
 
 @pytest.mark.parametrize("V,work", [(8, True), (6, True), (8, False)])
-@pytest.mark.parametrize("window", [1, 2, 31, 32, 33, 63, 64, 65, 72, 128, 129])
+@pytest.mark.parametrize("window", [1, 2, 31, 32, 33, 63, 64, 65, 80, 128, 129])
 def test_a_dominant_key_just_inside_and_just_outside_the_window(window, V, work):
     """One key is made to stand out (long, along every query); its value is a marker.  A query sees the marker exactly
     when 0 <= distance < window: in one portion (both kernels), across a portion border, and when decoding from the ring."""
@@ -494,7 +494,7 @@ def test_routed_experts_alone():
     """Sigmoid scores, several experts per token, the score as weight on the expert's input, the clamped unit: the
     device-indexed form (a few tokens) and the sorted form (many), f32 and bf16."""
     P, S, M = _pkg()
-    for (E, top, ff, D, limit) in ((6, 2, 40, 72, 1.0), (4, 1, 24, 64, 2.5), (9, 4, 20, 50, 0.5), (3, 3, 16, 32, 1.5)):
+    for (E, top, ff, D, limit) in ((6, 2, 40, 72, 1.0), (4, 1, 24, 64, 2.5), (9, 4, 20, 50, 0.5), (3, 3, 16, 32, 1.25)):
         m = moe(E, top, ff, limit)
         g = torch.Generator().manual_seed(E)
         W = {"router": (3.0 * torch.randn(E, D, generator=g) / math.sqrt(D)).bfloat16().float()}
