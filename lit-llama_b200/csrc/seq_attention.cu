@@ -188,6 +188,16 @@ __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_se
   const int p = pos0 + t, lo = first_visible(a, p) + c * DEC_CK;
   const int nv = min(DEC_CK, p - lo + 1);                         // keys of this chunk that the query sees
   float* part = a.work + ((size_t)(t * a.heads + g * hpg) * n_chunks + c) * (V + 2);      // head hq: + hq * n_chunks * (V + 2)
+  if (a.T == 1 && c == 0) {
+    // A single token appends itself to the ring here: its entry p % block holds a position that no query of this call
+    // sees (one ring turn back), and the chunks read the token's own key and value from k_new / v_new.
+    act_t* rk = (act_t*)a.cache_k + (((size_t)slot * a.block + p % a.block) * a.kv_heads + g) * a.K;
+    act_t* rv = (act_t*)a.cache_v + (((size_t)slot * a.block + p % a.block) * a.kv_heads + g) * a.V;
+    const act_t* nk = (const act_t*)a.k_new + (size_t)g * a.K;
+    const act_t* nvv = (const act_t*)a.v_new + (size_t)g * a.V;
+    for (int i = threadIdx.x; i < a.K; i += DEC_THREADS) rk[i] = nk[i];
+    for (int i = threadIdx.x; i < a.V; i += DEC_THREADS) rv[i] = nvv[i];
+  }
   if (nv <= 0) {
     for (int hq = tid; hq < hpg; hq += DEC_THREADS) {
       part[(size_t)hq * n_chunks * (V + 2)] = -INFINITY;
@@ -613,6 +623,7 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
       seq_attention_merge_kernel<float><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
     }
     B2L_LAUNCH_CHECK("seq_attention_chunk_kernel");
+    if (a->T == 1) return 0;                        // a single token was appended by its first chunk
     const int n_app0 = std::min(a->T, a->block);
     if (a->act_dtype == B2L_BF16) seq_ring_append_kernel<__nv_bfloat16><<<n_app0, 128, 0, s>>>(*a);
     else seq_ring_append_kernel<float><<<n_app0, 128, 0, s>>>(*a);
