@@ -37,7 +37,9 @@ __global__ void seq_embed_pair_kernel(const idx_t* __restrict__ tok, const act_t
     }
     __syncthreads();
     const long long prev = s_prev;
-    row = prev < 0 ? (long long)buckets : (long long)((unsigned long long)(prev * mul_prev + cur * mul_cur) % (unsigned long long)buckets);
+    // (prev * mul_prev + cur * mul_cur) mod buckets with every factor reduced first: no overflow for any multiplier
+    const long long b = buckets;
+    row = prev < 0 ? b : ((prev % b) * (mul_prev % b) + (cur % b) * (mul_cur % b)) % b;
   }
   const act_t* src = table + (size_t)cur * D;
   const act_t* add = row >= 0 ? pair + (size_t)row * D : nullptr;

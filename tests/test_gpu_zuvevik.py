@@ -87,7 +87,7 @@ def cfg_d():
 def cfg_e():
     d = cfg_d()
     d["streams"] = 5
-    d["embedding"] = {"bigram": {"buckets": 11, "mul_prev": 1000003, "mul_cur": 999983}}
+    d["embedding"] = {"bigram": {"buckets": 11, "mul_prev": 1000003, "mul_cur": (1 << 61) - 1}}
     return d
 
 
