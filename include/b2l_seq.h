@@ -45,8 +45,16 @@ int b2l_seq_norm_add_norm(const void* y, const void* w_post, float eps, float* x
 /* out[t, j] = act(gu[t, j]) * gu[t, F + j]  (gated feed-forward, both halves from one product).
  * B2L_SEQ_ACT_CLAMPED_SWISH is a gated unit with clamped halves: g = min(gu[t, j], limit),
  * u = clamp(gu[t, F + j], -limit, limit), out = g * sigmoid(1.702 g) * (u + 1).  `limit` is read by it alone. */
-enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2, B2L_SEQ_ACT_CLAMPED_SWISH = 3 };
+enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2, B2L_SEQ_ACT_CLAMPED_SWISH = 3, B2L_SEQ_ACT_XIELU = 4,
+       B2L_SEQ_ACT_NONE = 5 };
 int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, float limit, int act_dtype, b2l_stream_t stream);
+
+/* out[t, j] = act(in[t, j]) for an ungated feed-forward: gelu_tanh, silu, sigmoid, or B2L_SEQ_ACT_XIELU with its two
+ * learned numbers params = {p, q} (act, on the device), a = softplus(p), b = 1/2 + softplus(q):
+ *   z > 0: a z^2 + z / 2;   z <= 0: b (exp(z) - 1 - z) + z / 2.
+ * `params` is read by xIELU alone. */
+int b2l_seq_unary_act(const void* in, int ldin, void* out, int ldout, int T, int F, int act, const void* params, int act_dtype,
+                      b2l_stream_t stream);
 
 /* Short causal convolution over time per channel, then silu, with the last taps-1 inputs of the sequence carried
  * in `state` ([n_slots][taps-1][C] act, oldest first; a fresh slot holds zeros):
@@ -54,6 +62,26 @@ int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act
  * The state is advanced by the T tokens.  w is [C, taps] act, bias act or null, out f32. */
 int b2l_seq_conv_silu(const void* in, int ldin, const void* w, const void* bias, void* state, const int* meta,
                       float* out, int ldout, int T, int C, int taps, int act_dtype, b2l_stream_t stream);
+
+/* Attention operands from one stacked projection with a short causal convolution over time on every channel and a
+ * rotation by position afterwards.  proj (act [T, ld]) holds q at q_off (q_heads x K), and, unless k_off < 0 (a layer
+ * that attends over another layer's keys and values), k at k_off (k_heads x K) and v at v_off (n_v channels); all three
+ * lie inside the C convolved channels [c_off, c_off + C), every offset even.  Per channel c of those:
+ *   y[t, c] = sum_j w[c, j] * u[t - (taps - 1) + j, c]       (w act [C, taps], no bias, no activation)
+ * with the last taps-1 rows of u per sequence carried in `state` ([n_slots][taps-1][C] act, oldest first, zeros in a fresh
+ * slot) and advanced by the T tokens.  Then in every head of q and k the first rot_dims entries turn by the angle
+ * (pos0 + t) * freq[i], pairs (2i, 2i+1) when interleaved, else (i, i + rot_dims/2), cos and sin times rot_mult.
+ * q_out f32 [T, q_heads*K]; k_out act [T, k_heads*K]; v_out act [T, n_v]. */
+typedef struct {
+  const void* proj; int ld;
+  int c_off, C, taps;
+  const void* w; void* state; const int* meta;
+  int q_off, q_heads, k_off, k_heads, K, v_off, n_v;
+  const float* freq; int rot_dims, interleaved; float rot_mult;
+  float* q_out; void* k_out; void* v_out;
+  int T, act_dtype;
+} b2l_seq_conv_rope_args;
+int b2l_seq_conv_rope(const b2l_seq_conv_rope_args* a, b2l_stream_t stream);
 
 /* In place on f32: every block of `size` becomes x * mult / sqrt(sum(x^2) + eps). */
 int b2l_seq_unit_norm(float* x, int ld, int T, int heads, int size, float eps, float mult, b2l_stream_t stream);
@@ -130,12 +158,37 @@ typedef struct {
   int window;                     /* 0: block-local; > 0: sliding window of that many positions */
   int gate_per_channel;           /* gate is [T, heads*V] instead of [T, heads] */
   float* work; int work_floats;   /* optional f32 work space, see b2l_seq_block_attention_work_floats */
+  /* Several attention maps over the same values (maps > 1; 0 and 1 mean one): `heads` counts the maps of all query
+   * heads, laid out head by head as [map 0 | map 1 | ...] of K entries each; the keys likewise have kv_heads * maps
+   * heads of K entries, the values kv_heads heads of V entries.  Query map (h, m) reads key map m of its key/value head
+   * and that head's values; the maps' outputs lie side by side in `out` ([T, heads * V]) for the caller to combine. */
+  int maps;
+  int out_f32;                    /* out is f32 [T, ldo] instead of act */
+  int no_append;                  /* leave the ring as it is: the portion's keys and values are another layer's, which
+                                     appends them itself */
 } b2l_seq_attn_args;
 int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
 /* With few queries (decoding) the keys of a query are cut into chunks that run in parallel and are merged afterwards;
  * that form needs a work space of this many floats (0: this call does not use one).  Without `work` the call runs a
  * slower form that needs none.  The count depends on T, the head counts, V and the window or block, not on positions. */
 long long b2l_seq_block_attention_work_floats(const b2l_seq_attn_args* a);
+
+/* Differential read-out of two attention maps per head: a f32 [T, lda] holds per head [map 0 (V) | map 1 (V)];
+ *   o = a0 - lambda * a1;   out[t, h*V : (h+1)*V] = o / sqrt(mean(o^2) + eps) * mult      (act [T, ldo]) */
+int b2l_seq_diff_combine(const float* a, int lda, float lambda, float eps, float mult, void* out, int ldo, int T, int heads, int V,
+                         int act_dtype, b2l_stream_t stream);
+
+/* Gated recurrence on every channel by itself (minGRU): from one stacked projection proj (act [T, ld]) with the gate logits
+ * at z_off, the candidate inputs at x_off and the output gate at g_off (`width` channels each, biases already added):
+ *   z = sigmoid(proj_z);  c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), u = proj_x;  S_t = (1 - z) S_(t-1) + z c
+ *   out[t] = S_t * silu(proj_g)                                  (act [T, ldo]; g_off < 0: S_t itself)
+ * S lives per slot in `state` ([n_slots][width] f32, zeros in a fresh slot) and is advanced by the T tokens; everything
+ * after the projections is f32.  A long portion runs as n_chunks (> 1) chunks in parallel: every chunk's decay product and
+ * local end state, a short pass over the chunks, then the outputs; that form needs work: f32 [n_chunks][2][width].
+ * b2l_seq_mingru_chunks() says how many chunks a portion of T tokens wants (1 = sequential). */
+int b2l_seq_mingru_chunks(int T);
+int b2l_seq_mingru(const void* proj, int ld, int z_off, int x_off, int g_off, float* state, const int* meta, void* out, int ldo,
+                   float* work, int n_chunks, int T, int width, int act_dtype, b2l_stream_t stream);
 
 /* out[t, j] = (float) in[t, j]: act columns of a product as f32 operands of a recurrence. */
 int b2l_seq_cast_f32(const void* in, int ldin, float* out, int ldout, int T, int n, int act_dtype, b2l_stream_t stream);
@@ -156,10 +209,10 @@ int b2l_seq_softcap(float* z, size_t n, float cap, b2l_stream_t stream);
 
 /* Partial rotation by position, any layout.  Per head (`size` entries, heads every hsx elements of x and hso of out):
  * the entries [rot_off, rot_off + rot_dims) are rotated by the angle (pos0 + t) * freq[i]: pair (2i, 2i+1) when
- * interleaved, else (i, i + rot_dims/2); (u, v) -> (u cos - v sin, v cos + u sin).  Every entry is multiplied by
- * `mult` afterwards.  x is f32 (in_f32) or act, out f32 (out_f32) or act. */
+ * interleaved, else (i, i + rot_dims/2); (u, v) -> (u cos - v sin, v cos + u sin), cos and sin multiplied by
+ * rot_mult.  Every entry is multiplied by `mult` afterwards.  x is f32 (in_f32) or act, out f32 (out_f32) or act. */
 int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* freq, int rot_dims, int interleaved, int rot_off, float mult,
-                 const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size, int hsx, int hso, int act_dtype,
+                 float rot_mult, const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size, int hsx, int hso, int act_dtype,
                  b2l_stream_t stream);
 
 /* ---- latent attention ----
@@ -170,13 +223,15 @@ int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* freq, int rot_
  * b2l_seq_latent_prep, on the f32 product proj [T, ld] of the two down-projections:
  *   cq[t]  = rmsnorm(proj[t, q_off : q_off + q_rank]) * w_q                    (act [T, q_rank])
  *   cache[slot][pos0 + t] = [ rmsnorm(proj[t, kv_off : kv_off + rank]) * w_kv | rotate(proj[t, kv_off + rank : .. + rot_dim]) ]
- * with the rotation of b2l_seq_rope on the first rot_dims entries of the rotated part. */
+ * with the rotation of b2l_seq_rope on the first rot_dims entries of the rotated part (cos and sin times rot_mult). */
 int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_rank, const void* w_q, void* cq, int kv_off, int rank,
-                        const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved, float eps,
+                        const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved, float rot_mult, float eps,
                         const int* meta, void* cache, int max_pos, int T, int act_dtype, b2l_stream_t stream);
 
-/* Causal softmax attention with a learned sink per head over keys 0 .. pos0 + t:
+/* Causal softmax attention with a learned sink per head over keys 0 .. pos0 + t, or, with window > 0, over the keys
+ * pos0 + t - window + 1 .. pos0 + t (the query's own position and the window - 1 before it):
  *   weights exp(score_j) / (exp(sink[h]) + sum_j exp(score_j)),  score = (q . key_j[score_off:]) * scale
+ *   (sink null: ordinary softmax, no sink term)
  *   out[t, h*vdim : (h+1)*vdim] = sum_j weight_j key_j[0 : vdim]
  * A key row is [A (n_a entries) | B (n_b entries)]: A belongs to a key group (row j at key_a + slot*slot_stride_a +
  * group*hska + j*ldka), B is shared by all groups (key_b + slot*slot_stride_b + j*ldkb); heads_per_group consecutive
@@ -194,12 +249,13 @@ typedef struct {
   const float* q_b; long long ldqb_t; long long ldqb_h;
   const void* key_a; long long ldka; long long hska; long long slot_stride_a;
   const void* key_b; long long ldkb; long long slot_stride_b;
-  const float* sink;               /* f32 [heads] */
+  const float* sink;               /* f32 [heads], or null */
   const int* meta;
   void* out; int ldo;              /* act [T, ldo] */
   float* work;
   float scale;
   int T, heads, heads_per_group, n_a, n_b, vdim, score_off, splits, act_dtype;
+  int window;                      /* 0: every earlier position; > 0: a sliding window of that many positions */
 } b2l_seq_latent_attn_args;
 int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream);
 int b2l_seq_latent_attention_warps(int T, int heads_per_group);    /* warps per CTA that own rows: 4 rows per warp */
@@ -207,17 +263,18 @@ int b2l_seq_latent_attention_warps(int T, int heads_per_group);    /* warps per 
 /* ---- mixture of experts ----
  * Router, per token, from f32 logits [T, ld] over n experts: s = softmax(logits) over the experts, or sigmoid(logits)
  * of each (score_fn); choice = s + correction (f32 [n], may be null); the n experts form `groups` equal groups of
- * neighbours, a group's score is its largest choice score, only experts of the `keep` best groups can be chosen;
+ * neighbours, a group's score is the sum of its `group_top` largest choice scores (1: its largest), only experts of the
+ * `keep` best groups can be chosen (ties to the lower group);
  * idx[t, :] = the `top` largest choice scores among them (best first, ties to the lower index);
- * weights[t, k] = s[idx] / (sum of the chosen s + 1e-20) when `renormalize`, else s[idx] itself. */
+ * weights[t, k] = weight_scale * s[idx] / (sum of the chosen s + 1e-20) when `renormalize`, else weight_scale * s[idx]. */
 enum { B2L_SEQ_SCORE_SOFTMAX = 0, B2L_SEQ_SCORE_SIGMOID = 1 };
 int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int score_fn,
-                      int renormalize, int* idx, float* weights, int T, b2l_stream_t stream);
+                      int renormalize, int group_top, float weight_scale, int* idx, float* weights, int T, b2l_stream_t stream);
 
 /* The same with the logits computed in the kernel, for a few tokens: logits[t] = w_router h[t] (w_router act [n][D],
  * f32 accumulation), one CTA per token, one launch for product and routing. */
 int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups, int keep,
-                            int top, int score_fn, int renormalize, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream);
+                            int top, int score_fn, int renormalize, int group_top, float weight_scale, int* idx, float* weights, int T, int act_dtype, b2l_stream_t stream);
 
 /* Experts of a few tokens, indices read on the device.  Expert e < n_real: W_down[e] (gated(W_gate[e] h, W_up[e] h))
  * with w_gate_up act [n_real][2*ff][D] (gate rows, then up rows), w_down act [n_real][D][ff] and the gated unit of
@@ -262,6 +319,24 @@ int b2l_seq_hc_step(const void* y, float* X, const float* mix, const float* out_
                     float eps, const int* rows, int n_rows, int D, int streams, int act_dtype, b2l_stream_t stream);
 /* out[t, :] = sum_s X[t, s, :]. */
 int b2l_seq_hc_sum(const float* X, float* out, int T, int D, int streams, b2l_stream_t stream);
+
+/* ---- norms with a bias, depth-weighted residual ----
+ * out[r] = norm(x[rows[r]]) (rows null: row r), x f32 [*, D] -> out act [n_rows, D]:
+ *   B2L_SEQ_NORM_RMS:   x / sqrt(mean(x^2) + eps) * w (+ b when given)
+ *   B2L_SEQ_NORM_LAYER: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b      (b may be null) */
+enum { B2L_SEQ_NORM_RMS = 0, B2L_SEQ_NORM_LAYER = 1 };
+int b2l_seq_norm(const float* x, const void* w, const void* b, int kind, float eps, void* out, const int* rows, int n_rows, int D,
+                 int act_dtype, b2l_stream_t stream);
+
+/* One layer's residual step when the next layer reads a learned average over everything earlier layers produced.
+ * hist f32 [n_hist][T][D] holds the embedding output (entry 0) and the own results of the layers so far; this call
+ *   writes the layer's own result      hist[n_hist - 1] = x_in + y1 + y2        (y1, y2 act [T, D]; y2 may be null)
+ *   forms the next layer's input       x_out = sum_j avg[j] * hist[j], j < n_hist   (avg f32 [n_hist]; null: hist[n_hist - 1])
+ *   and, with w_next, its norm         h = norm(x_out) as b2l_seq_norm (act [T, D])
+ * x_in and x_out may be the same buffer.  With y1 null only the average and the norm are done (n_hist entries exist). */
+int b2l_seq_depth_step(const void* y1, const void* y2, const float* x_in, float* hist, int n_hist, const float* avg, float* x_out,
+                       const void* w_next, const void* b_next, int norm_kind, float eps, void* h, int T, int D, int act_dtype,
+                       b2l_stream_t stream);
 
 /* z <- z * mult in place on f32 (a constant scale of the logits). */
 int b2l_seq_scale(float* z, size_t n, float mult, b2l_stream_t stream);

@@ -20,7 +20,8 @@ LIBRARIES = {
                            "q8_gemv.cu", "sampling.cu", "decode_mega.cu", "q4_gemm.cu", "tp_allreduce.cu"]),
     # sequence-mixer kernels: recurrences, local and latent attention, expert routing, f32 residual streams (include/b2l_seq.h)
     "seq": dict(out=os.path.join(PKG, "libb200seq.so"),
-                sources=["seq_api.cu", "seq_elementwise.cu", "seq_scan.cu", "seq_attention.cu", "seq_latent.cu", "seq_moe.cu", "seq_streams.cu"]),
+                sources=["seq_api.cu", "seq_elementwise.cu", "seq_scan.cu", "seq_attention.cu", "seq_latent.cu", "seq_moe.cu", "seq_streams.cu",
+                         "seq_depth.cu", "seq_gru.cu", "seq_convrope.cu"]),
 }
 
 

@@ -16,6 +16,7 @@ from .tp import TPLLaMA, shard_state_dict
 from .lugovik import Lugovik, LugovikConfig
 from .zenasun import Zenasun, ZenasunConfig
 from .zuvevik import Zuvevik, ZuvevikConfig
+from .rinirax import Rinirax, RiniraxConfig
 from .state import SequenceStatePool, StateSpec
 from .engine import Engine
 from .registry import load_model, register
@@ -23,5 +24,6 @@ from .registry import load_model, register
 __all__ = [
     "LLaMA", "LLaMAConfig", "Block", "CausalSelfAttention", "MLP", "RMSNorm", "build_rope_cache", "apply_rope",
     "ColBlockQuantizedLinear", "Linear8bitLt", "find_multiple", "llama_model_lookup", "generate", "sample_probs", "sample_token", "patch_reference", "TPLLaMA", "shard_state_dict",
-    "Lugovik", "LugovikConfig", "Zenasun", "ZenasunConfig", "Zuvevik", "ZuvevikConfig", "SequenceStatePool", "StateSpec", "Engine", "load_model", "register",
+    "Lugovik", "LugovikConfig", "Zenasun", "ZenasunConfig", "Zuvevik", "ZuvevikConfig", "Rinirax", "RiniraxConfig",
+    "SequenceStatePool", "StateSpec", "Engine", "load_model", "register",
 ]

@@ -8,7 +8,8 @@ import torch
 from . import _build
 
 B2L_BF16, B2L_F32 = 0, 1
-ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_CLAMPED_SWISH = 0, 1, 2, 3
+ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_CLAMPED_SWISH, ACT_XIELU, ACT_NONE = 0, 1, 2, 3, 4, 5
+NORM_RMS, NORM_LAYER = 0, 1
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 DECAY_EXP_SOFTPLUS, DECAY_SIGMOID_ROOT = 0, 1
 
@@ -46,6 +47,7 @@ class AttnArgs(C.Structure):
         ("act_dtype", c_int),
         ("window", c_int), ("gate_per_channel", c_int),
         ("work", c_void_p), ("work_floats", c_int),
+        ("maps", c_int), ("out_f32", c_int), ("no_append", c_int),
     ]
 
 
@@ -62,6 +64,19 @@ class LatentAttnArgs(C.Structure):
         ("scale", c_float),
         ("T", c_int), ("heads", c_int), ("heads_per_group", c_int), ("n_a", c_int), ("n_b", c_int), ("vdim", c_int), ("score_off", c_int),
         ("splits", c_int), ("act_dtype", c_int),
+        ("window", c_int),
+    ]
+
+
+class ConvRopeArgs(C.Structure):
+    _fields_ = [
+        ("proj", c_void_p), ("ld", c_int),
+        ("c_off", c_int), ("C", c_int), ("taps", c_int),
+        ("w", c_void_p), ("state", c_void_p), ("meta", c_void_p),
+        ("q_off", c_int), ("q_heads", c_int), ("k_off", c_int), ("k_heads", c_int), ("K", c_int), ("v_off", c_int), ("n_v", c_int),
+        ("freq", c_void_p), ("rot_dims", c_int), ("interleaved", c_int), ("rot_mult", c_float),
+        ("q_out", c_void_p), ("k_out", c_void_p), ("v_out", c_void_p),
+        ("T", c_int), ("act_dtype", c_int),
     ]
 
 
@@ -102,15 +117,16 @@ _SIGS = {
     "b2l_seq_add_norm2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
                                   c_int, c_int, c_void_p]),
     "b2l_seq_softcap": (c_int, [c_void_p, c_size_t, c_float, c_void_p]),
-    "b2l_seq_rope": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+    "b2l_seq_rope": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_latent_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
-                                    c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+                                    c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_latent_attention": (c_int, [C.POINTER(LatentAttnArgs), c_void_p]),
     "b2l_seq_latent_attention_warps": (c_int, [c_int, c_int]),
-    "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
-    "b2l_seq_moe_route_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                        c_int, c_int, c_void_p]),
+    "b2l_seq_moe_route": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                  c_void_p]),
+    "b2l_seq_moe_route_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                        c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b2l_seq_moe_experts_small": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
     "b2l_seq_moe_sort": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -123,6 +139,15 @@ _SIGS = {
     "b2l_seq_hc_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b2l_seq_scale": (c_int, [c_void_p, c_size_t, c_float, c_void_p]),
     "b2l_seq_qkv_prep": (c_int, [C.POINTER(QkvPrepArgs), c_void_p]),
+    "b2l_seq_unary_act": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "b2l_seq_conv_rope": (c_int, [C.POINTER(ConvRopeArgs), c_void_p]),
+    "b2l_seq_diff_combine": (c_int, [c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_mingru_chunks": (c_int, [c_int]),
+    "b2l_seq_mingru": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                               c_void_p]),
+    "b2l_seq_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b2l_seq_depth_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                   c_void_p, c_int, c_int, c_int, c_void_p]),
 }
 
 EXPORTS = tuple(_SIGS)

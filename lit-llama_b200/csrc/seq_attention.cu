@@ -10,11 +10,30 @@
 // warp kernel (single tokens, and shapes the tiled kernel does not take): WPQ warps per (query, head).  A warp takes batches of 32 consecutive keys: each lane scores one
 // key (q from shared memory, its key row by 16-byte loads), the batch maximum and the weights go through shuffles,
 // and the value rows are accumulated with lanes over value channels.  Scores, weights and accumulators are f32.
+//
+// Several maps over the same values (maps > 1): every query head and every key head carries `maps` score vectors of K
+// entries; each map is a softmax attention of its own and is handled as a head of its own ("virtual head" h = real
+// head * maps + map) that reads key map (h % maps) of its key/value head and that head's values.  The maps' outputs are
+// stored side by side; combining them (for instance the difference of two maps) is the caller's next kernel.
 #include "seq_common.cuh"
 
 namespace b2l {
 
 constexpr int ATT_VMAX = 8;   // value channels per lane: V <= 256
+
+// Key head and value head of (virtual) query head h.
+__device__ __forceinline__ void kv_heads_of(const b2l_seq_attn_args& a, int h, int& gk, int& gv) {
+  const int maps = a.maps > 1 ? a.maps : 1;
+  const int hr = h / maps;
+  gv = hr / ((a.heads / maps) / a.kv_heads);
+  gk = gv * maps + (h - hr * maps);
+}
+
+template <typename act_t>
+__device__ __forceinline__ void st_out(const b2l_seq_attn_args& a, size_t i, float v) {
+  if (a.out_f32) reinterpret_cast<float*>(a.out)[i] = v;
+  else st_act(reinterpret_cast<act_t*>(a.out), i, v);
+}
 
 // The first position a query at position p sees.
 __device__ __forceinline__ int first_visible(const b2l_seq_attn_args& a, int p) {
@@ -71,7 +90,9 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
   const int pair = blockIdx.x * QPC + warp / WPQ, sub = warp % WPQ;
   const bool live = pair < a.T * a.heads;
   const int t = live ? pair / a.heads : 0, h = live ? pair % a.heads : 0;
-  const int g = h / (a.heads / a.kv_heads);
+  int gk, gv;
+  kv_heads_of(a, h, gk, gv);
+  const int kh = a.kv_heads * (a.maps > 1 ? a.maps : 1);
   const int slot = a.meta[0], pos0 = a.meta[1];
   const int p = pos0 + t, c0 = first_visible(a, p);
 
@@ -82,7 +103,7 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
 
   const act_t* kn = (const act_t*)a.k_new;
   const act_t* vn = (const act_t*)a.v_new;
-  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
+  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * kh * K;
   const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
 
   float m = a.has_sink ? 0.f : -INFINITY, l = (a.has_sink && sub == 0) ? 1.f : 0.f;
@@ -95,8 +116,8 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
       const int j = jb + lane;
       float s = -INFINITY;
       if (j <= p) {
-        const act_t* kr = j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K
-                                    : ck + ((size_t)(j % a.block) * a.kv_heads + g) * K;
+        const act_t* kr = j >= pos0 ? kn + ((size_t)(j - pos0) * kh + gk) * K
+                                    : ck + ((size_t)(j % a.block) * kh + gk) * K;
         s = dot_row<act_t>(myq, kr, K, vec != 0) * a.scale;
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
       }
@@ -112,8 +133,8 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
       for (int jj = 0; jj < 32; ++jj) {
         const float wj = __shfl_sync(0xffffffffu, w, jj);      // 0 beyond the last key of the batch
         const int jv = jb + min(jj, nb - 1);                    // a valid row for the masked tail (weight 0)
-        const act_t* vr = jv >= pos0 ? vn + (size_t)(jv - pos0) * a.ldv + (size_t)g * V
-                                     : cv + ((size_t)(jv % a.block) * a.kv_heads + g) * V;
+        const act_t* vr = jv >= pos0 ? vn + (size_t)(jv - pos0) * a.ldv + (size_t)gv * V
+                                     : cv + ((size_t)(jv % a.block) * a.kv_heads + gv) * V;
 #pragma unroll
         for (int c = 0; c < ATT_VMAX; ++c) {
           const int ch = c * 32 + lane;
@@ -147,11 +168,11 @@ __global__ void __launch_bounds__(WPQ > 4 ? 32 * WPQ : 128) seq_block_attention_
   float f = a.out_mult / l;
   const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
   if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
-  act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
+  const size_t o = (size_t)t * a.ldo + (size_t)h * V;
 #pragma unroll
   for (int c = 0; c < ATT_VMAX; ++c) {
     const int ch = c * 32 + lane;
-    if (ch < V) st_act(o, ch, acc[c] * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
+    if (ch < V) st_out<act_t>(a, o + ch, acc[c] * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
   }
 }
 
@@ -176,7 +197,8 @@ template <typename act_t>
 __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_seq_attn_args a, int n_chunks, int vec) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   constexpr int PER = 16 / (int)sizeof(act_t);
-  const int K = a.K, V = a.V, Kpa = K + PER, hpg = a.heads / a.kv_heads;
+  const int maps = a.maps > 1 ? a.maps : 1;
+  const int K = a.K, KR = K * maps, V = a.V, Kpa = KR + PER, hpg = a.heads / a.kv_heads;      // a key row holds the maps side by side
   const int Vp = (V + PER - 1) / PER * PER;
   act_t* sK = reinterpret_cast<act_t*>(dec_smem);                 // [DEC_CK][Kpa]
   act_t* sV = sK + DEC_CK * Kpa;                                  // [DEC_CK][Vp]
@@ -188,14 +210,14 @@ __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_se
   const int p = pos0 + t, lo = first_visible(a, p) + c * DEC_CK;
   const int nv = min(DEC_CK, p - lo + 1);                         // keys of this chunk that the query sees
   float* part = a.work + ((size_t)(t * a.heads + g * hpg) * n_chunks + c) * (V + 2);      // head hq: + hq * n_chunks * (V + 2)
-  if (a.T == 1 && c == 0) {
+  if (a.T == 1 && c == 0 && !a.no_append) {
     // A single token appends itself to the ring here: its entry p % block holds a position that no query of this call
     // sees (one ring turn back), and the chunks read the token's own key and value from k_new / v_new.
-    act_t* rk = (act_t*)a.cache_k + (((size_t)slot * a.block + p % a.block) * a.kv_heads + g) * a.K;
+    act_t* rk = (act_t*)a.cache_k + (((size_t)slot * a.block + p % a.block) * a.kv_heads + g) * KR;
     act_t* rv = (act_t*)a.cache_v + (((size_t)slot * a.block + p % a.block) * a.kv_heads + g) * a.V;
-    const act_t* nk = (const act_t*)a.k_new + (size_t)g * a.K;
+    const act_t* nk = (const act_t*)a.k_new + (size_t)g * KR;
     const act_t* nvv = (const act_t*)a.v_new + (size_t)g * a.V;
-    for (int i = threadIdx.x; i < a.K; i += DEC_THREADS) rk[i] = nk[i];
+    for (int i = threadIdx.x; i < KR; i += DEC_THREADS) rk[i] = nk[i];
     for (int i = threadIdx.x; i < a.V; i += DEC_THREADS) rv[i] = nvv[i];
   }
   if (nv <= 0) {
@@ -207,22 +229,22 @@ __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_se
   }
   const act_t* kn = (const act_t*)a.k_new;
   const act_t* vn = (const act_t*)a.v_new;
-  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
+  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * KR;
   const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
   if (vec) {
-    const int kc = K / PER, vc = V / PER;
+    const int kc = KR / PER, vc = V / PER;
     for (int i = tid; i < nv * kc; i += DEC_THREADS) {
       const int r = i / kc, e = (i - r * kc) * PER, j = lo + r;
-      dec_cp_async16(sK + r * Kpa + e, j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + e : ck + ((size_t)(j % a.block) * a.kv_heads + g) * K + e);
+      dec_cp_async16(sK + r * Kpa + e, j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * KR + e : ck + ((size_t)(j % a.block) * a.kv_heads + g) * KR + e);
     }
     for (int i = tid; i < nv * vc; i += DEC_THREADS) {
       const int r = i / vc, e = (i - r * vc) * PER, j = lo + r;
       dec_cp_async16(sV + r * Vp + e, j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + e : cv + ((size_t)(j % a.block) * a.kv_heads + g) * V + e);
     }
   } else {
-    for (int i = tid; i < nv * K; i += DEC_THREADS) {
-      const int r = i / K, e = i - r * K, j = lo + r;
-      sK[r * Kpa + e] = j >= pos0 ? kn[((size_t)(j - pos0) * a.kv_heads + g) * K + e] : ck[((size_t)(j % a.block) * a.kv_heads + g) * K + e];
+    for (int i = tid; i < nv * KR; i += DEC_THREADS) {
+      const int r = i / KR, e = i - r * KR, j = lo + r;
+      sK[r * Kpa + e] = j >= pos0 ? kn[((size_t)(j - pos0) * a.kv_heads + g) * KR + e] : ck[((size_t)(j % a.block) * a.kv_heads + g) * KR + e];
     }
     for (int i = tid; i < nv * V; i += DEC_THREADS) {
       const int r = i / V, e = i - r * V, j = lo + r;
@@ -236,7 +258,7 @@ __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_se
     const int hq = i / DEC_CK, r = i - hq * DEC_CK;
     float sc = -INFINITY;
     if (r < nv) {
-      sc = dot_row<act_t>(sQ + hq * K, sK + r * Kpa, K, vec != 0) * a.scale;
+      sc = dot_row<act_t>(sQ + hq * K, sK + r * Kpa + (hq % maps) * K, K, vec != 0) * a.scale;      // the group's first head is a multiple of maps
       if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
     }
     sS[i] = sc;
@@ -309,7 +331,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_
   float f = a.out_mult / l;
   const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
   if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
-  act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
+  const size_t o = (size_t)t * a.ldo + (size_t)h * V;
   for (int ch = tid; ch < V; ch += MERGE_THREADS) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int c = 0;
@@ -326,7 +348,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_
       if (fc != 0.f) acc[0] = fmaf(part[(size_t)c * (V + 2) + 2 + ch], fc, acc[0]);
     }
     const float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    st_act(o, ch, sum * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
+    st_out<act_t>(a, o + ch, sum * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
   }
 }
 
@@ -334,7 +356,8 @@ template <typename act_t>
 static size_t chunk_smem_bytes(const b2l_seq_attn_args* a) {
   const int per = 16 / (int)sizeof(act_t), hpg = a->heads / a->kv_heads;
   const int Vp = (a->V + per - 1) / per * per;
-  return sizeof(act_t) * ((size_t)DEC_CK * (a->K + per) + (size_t)DEC_CK * Vp) + sizeof(float) * ((size_t)hpg * a->K + (size_t)hpg * DEC_CK);
+  const int KR = a->K * (a->maps > 1 ? a->maps : 1);
+  return sizeof(act_t) * ((size_t)DEC_CK * (KR + per) + (size_t)DEC_CK * Vp) + sizeof(float) * ((size_t)hpg * a->K + (size_t)hpg * DEC_CK);
 }
 static int chunk_count(const b2l_seq_attn_args* a) { return ((a->window > 0 ? a->window : a->block) + DEC_CK - 1) / DEC_CK; }
 static bool few_queries(const b2l_seq_attn_args* a) { return a->T * a->heads < 2 * sm_count(); }
@@ -376,7 +399,9 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
   sKb = reinterpret_cast<act_t*>((reinterpret_cast<uintptr_t>(sKb)) & ~(uintptr_t)15);
   act_t* sVb = sKb + 2 * TK * Kpa;                        // 2 x [TK][V]
   const int tid = threadIdx.x, ty = tid >> 3, tx = tid & 7;
-  const int h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+  const int h = blockIdx.y, kh = a.kv_heads * (a.maps > 1 ? a.maps : 1);
+  int gk, gv;
+  kv_heads_of(a, h, gk, gv);
   const int qt = gridDim.x - 1 - blockIdx.x;              // the longest tiles (last queries of a block) start first
   const int t_first = qt * TQ, nq = min(TQ, a.T - t_first);
   const int slot = a.meta[0], pos0 = a.meta[1];
@@ -386,7 +411,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
 
   const act_t* kn = (const act_t*)a.k_new;
   const act_t* vn = (const act_t*)a.v_new;
-  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * a.kv_heads * K;
+  const act_t* ck = (const act_t*)a.cache_k + (size_t)slot * a.block * kh * K;
   const act_t* cv = (const act_t*)a.cache_v + (size_t)slot * a.block * a.kv_heads * V;
 
   auto issue_tile = [&](int jb, int buf) {
@@ -397,7 +422,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
       const int r = i / kc, c = (i - r * kc) * PER, j = jb + r;
       if (j <= p_last) {
         const int e = j % a.block;
-        att_cp_async16(dK + r * Kpa + c, j >= pos0 ? kn + ((size_t)(j - pos0) * a.kv_heads + g) * K + c : ck + ((size_t)e * a.kv_heads + g) * K + c);
+        att_cp_async16(dK + r * Kpa + c, j >= pos0 ? kn + ((size_t)(j - pos0) * kh + gk) * K + c : ck + ((size_t)e * kh + gk) * K + c);
       } else {
         *reinterpret_cast<uint4*>(dK + r * Kpa + c) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -406,7 +431,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
       const int r = i / vc, c = (i - r * vc) * PER, j = jb + r;
       if (j <= p_last) {
         const int e = j % a.block;
-        att_cp_async16(dV + r * V + c, j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)g * V + c : cv + ((size_t)e * a.kv_heads + g) * V + c);
+        att_cp_async16(dV + r * V + c, j >= pos0 ? vn + (size_t)(j - pos0) * a.ldv + (size_t)gv * V + c : cv + ((size_t)e * a.kv_heads + gv) * V + c);
       } else {
         *reinterpret_cast<uint4*>(dV + r * V + c) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -529,7 +554,7 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
     float f = a.out_mult / l[i];
     const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
     if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
-    act_t* o = (act_t*)a.out + (size_t)t * a.ldo + (size_t)h * V;
+    const size_t o = (size_t)t * a.ldo + (size_t)h * V;
 #pragma unroll
     for (int c = 0; c < VC; ++c) {
       const int ch = tx * 4 + 32 * c;
@@ -539,8 +564,8 @@ __global__ void __launch_bounds__(TILE_THREADS) seq_block_attention_tile_kernel(
         const float4 gv = ld4_act<act_t>(gate + (size_t)h * V + ch);      // 16-byte aligned rows of 4-channel groups: checked by the launcher
         gq[0] *= sigmoid_f(gv.x); gq[1] *= sigmoid_f(gv.y); gq[2] *= sigmoid_f(gv.z); gq[3] *= sigmoid_f(gv.w);
       }
-      st_act(o, ch + 0, acc[i][c][0] * gq[0]); st_act(o, ch + 1, acc[i][c][1] * gq[1]);
-      st_act(o, ch + 2, acc[i][c][2] * gq[2]); st_act(o, ch + 3, acc[i][c][3] * gq[3]);
+      st_out<act_t>(a, o + ch + 0, acc[i][c][0] * gq[0]); st_out<act_t>(a, o + ch + 1, acc[i][c][1] * gq[1]);
+      st_out<act_t>(a, o + ch + 2, acc[i][c][2] * gq[2]); st_out<act_t>(a, o + ch + 3, acc[i][c][3] * gq[3]);
     }
   }
 }
@@ -573,7 +598,7 @@ __global__ void seq_ring_append_kernel(b2l_seq_attn_args a) {
   const int p = first + blockIdx.x;
   if (p > last) return;
   const int t = p - pos0, e = p % a.block;
-  const int nk = a.kv_heads * a.K, nv = a.kv_heads * a.V;
+  const int nk = a.kv_heads * (a.maps > 1 ? a.maps : 1) * a.K, nv = a.kv_heads * a.V;
   const act_t* kn = (const act_t*)a.k_new + (size_t)t * nk;
   const act_t* vn = (const act_t*)a.v_new + (size_t)t * a.ldv;
   act_t* ck = (act_t*)a.cache_k + ((size_t)slot * a.block + e) * nk;
@@ -582,15 +607,54 @@ __global__ void seq_ring_append_kernel(b2l_seq_attn_args a) {
   for (int i = threadIdx.x; i < nv; i += blockDim.x) cv[i] = vn[i];
 }
 
+// Differential read-out: one warp per (token, head): o = a0 - lambda a1, divided by its root mean square, times mult.
+template <typename act_t>
+__global__ void seq_diff_combine_kernel(const float* __restrict__ a, int lda, float lambda, float eps, float mult, act_t* __restrict__ out,
+                                        int ldo, int n_rows, int heads, int V) {
+  const int id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (id >= n_rows * heads) return;
+  const int t = id / heads, h = id - t * heads;
+  const float* p = a + (size_t)t * lda + (size_t)h * 2 * V;
+  float o[ATT_VMAX], ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < ATT_VMAX; ++c) {
+    const int ch = c * 32 + lane;
+    o[c] = ch < V ? p[ch] - lambda * p[V + ch] : 0.f;
+    ss += o[c] * o[c];
+  }
+  ss = warp_sum(ss);
+  const float r = mult / sqrtf(ss / (float)V + eps);
+  act_t* q = out + (size_t)t * ldo + (size_t)h * V;
+#pragma unroll
+  for (int c = 0; c < ATT_VMAX; ++c) {
+    const int ch = c * 32 + lane;
+    if (ch < V) st_act(q, ch, o[c] * r);
+  }
+}
+
 }  // namespace b2l
 
 using namespace b2l;
+
+extern "C" int b2l_seq_diff_combine(const float* a, int lda, float lambda, float eps, float mult, void* out, int ldo, int T, int heads, int V,
+                                    int act_dtype, b2l_stream_t stream) {
+  B2L_CHECK_ARG(a && out, "b2l_seq_diff_combine: null pointer");
+  B2L_CHECK_ARG(T >= 0 && heads > 0 && V > 0 && lda >= heads * 2 * V && ldo >= heads * V, "b2l_seq_diff_combine: bad size");
+  B2L_CHECK_SUPPORTED(V <= ATT_VMAX * 32, "b2l_seq_diff_combine: value size %d above %d", V, ATT_VMAX * 32);
+  if (T == 0) return 0;
+  const int ids = T * heads;
+  B2L_SEQ_DISPATCH(act_dtype, (seq_diff_combine_kernel<act_t><<<(ids + 3) / 4, 128, 0, (cudaStream_t)stream>>>(a, lda, lambda, eps, mult, (act_t*)out, ldo, T, heads, V)));
+  B2L_LAUNCH_CHECK("seq_diff_combine_kernel");
+  return 0;
+}
 
 extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream) {
   B2L_CHECK_ARG(a != nullptr, "b2l_seq_block_attention: null argument block");
   B2L_CHECK_ARG(a->q && a->k_new && a->v_new && a->cache_k && a->cache_v && a->meta && a->out, "b2l_seq_block_attention: null pointer");
   B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->kv_heads > 0 && a->K > 0 && a->V > 0 && a->block > 0, "b2l_seq_block_attention: bad size");
-  B2L_CHECK_ARG(a->heads % a->kv_heads == 0, "b2l_seq_block_attention: heads %d not a multiple of kv_heads %d", a->heads, a->kv_heads);
+  B2L_CHECK_ARG(a->maps >= 0 && a->heads % (a->kv_heads * (a->maps > 1 ? a->maps : 1)) == 0,
+                "b2l_seq_block_attention: heads %d not a multiple of kv_heads %d times maps %d", a->heads, a->kv_heads, a->maps);
+  B2L_CHECK_ARG(!(a->gate && a->out_f32), "b2l_seq_block_attention: a gated output is stored in the activation type");
   B2L_CHECK_ARG(a->window >= 0 && (a->window == 0 || a->block >= a->window), "b2l_seq_block_attention: a ring of %d positions cannot serve a window of %d",
                 a->block, a->window);
   B2L_CHECK_SUPPORTED(a->V <= ATT_VMAX * 32, "b2l_seq_block_attention: value size %d above %d", a->V, ATT_VMAX * 32);
@@ -623,7 +687,7 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
       seq_attention_merge_kernel<float><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
     }
     B2L_LAUNCH_CHECK("seq_attention_chunk_kernel");
-    if (a->T == 1) return 0;                        // a single token was appended by its first chunk
+    if (a->T == 1 || a->no_append) return 0;        // a single token was appended by its first chunk
     const int n_app0 = std::min(a->T, a->block);
     if (a->act_dtype == B2L_BF16) seq_ring_append_kernel<__nv_bfloat16><<<n_app0, 128, 0, s>>>(*a);
     else seq_ring_append_kernel<float><<<n_app0, 128, 0, s>>>(*a);
@@ -655,6 +719,7 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
     else seq_block_attention_kernel<float, 1><<<(pairs + 3) / 4, 128, smem, s>>>(*a, vec);
   }
   B2L_LAUNCH_CHECK("seq_block_attention_kernel");
+  if (a->no_append) return 0;
   const int n_app = std::min(a->T, a->block);
   if (a->act_dtype == B2L_BF16) seq_ring_append_kernel<__nv_bfloat16><<<n_app, 128, 0, s>>>(*a);
   else seq_ring_append_kernel<float><<<n_app, 128, 0, s>>>(*a);

@@ -7,8 +7,11 @@
 //  - expanded form, for long portions: the caller expands [value_h | key_h] of every cached position with one
 //    product, and every head attends over its own rows plus the shared rotated part: 3-4 times fewer operations
 //    per (query, key) pair when the latent is several times wider than a head.
-// Softmax has one learned sink per head in the denominator (exp(sink_h), no key, no value).  Scores, weights and
-// accumulators are f32.
+// Softmax has one learned sink per head in the denominator (exp(sink_h), no key, no value) when a sink is given.  With
+// a window a row sees its own position and the window - 1 before it; a CTA then walks only the keys between the first
+// key of its first row and the last key of its last row.  Scores, weights and accumulators are f32.
+#include <climits>
+
 #include "seq_common.cuh"
 
 namespace b2l {
@@ -18,7 +21,7 @@ namespace b2l {
 // `mult` afterwards.  Heads start every hsx (input) / hso (output) elements.  One warp per (token, head).
 template <typename in_t, typename out_t>
 __global__ void seq_rope_kernel(const in_t* __restrict__ x, int ldx, const float* __restrict__ freq, int rot_dims, int interleaved,
-                                int off, float mult, const int* __restrict__ meta, out_t* __restrict__ out, int ldo, int n_rows, int heads,
+                                int off, float mult, float rot_mult, const int* __restrict__ meta, out_t* __restrict__ out, int ldo, int n_rows, int heads,
                                 int size, int hsx, int hso) {
   const int id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (id >= n_rows * heads) return;
@@ -33,6 +36,8 @@ __global__ void seq_rope_kernel(const in_t* __restrict__ x, int ldx, const float
     const float u = ld_act(p, iu), v = ld_act(p, iv);
     float s, c;
     sincosf(pos * freq[i], &s, &c);
+    s *= rot_mult;
+    c *= rot_mult;
     st_act(q, iu, (u * c - v * s) * mult);
     st_act(q, iv, (v * c + u * s) * mult);
   }
@@ -47,8 +52,8 @@ template <typename act_t>
 __global__ void __launch_bounds__(128) seq_latent_prep_kernel(const float* __restrict__ proj, int ld, int q_off, int q_rank,
                                                               const act_t* __restrict__ wq, act_t* __restrict__ cq, int kv_off, int rank,
                                                               const act_t* __restrict__ wkv, int rot_dim, const float* __restrict__ freq,
-                                                              int rot_dims, int interleaved, float eps, const int* __restrict__ meta,
-                                                              act_t* __restrict__ cache, int max_pos) {
+                                                              int rot_dims, int interleaved, float rot_mult, float eps,
+                                                              const int* __restrict__ meta, act_t* __restrict__ cache, int max_pos) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const float* row = proj + (size_t)t * ld;
@@ -76,6 +81,8 @@ __global__ void __launch_bounds__(128) seq_latent_prep_kernel(const float* __res
     const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
     float s, c;
     sincosf((float)pos * freq[i], &s, &c);
+    s *= rot_mult;
+    c *= rot_mult;
     st_act(dst, rank + iu, b[iu] * c - b[iv] * s);
     st_act(dst, rank + iv, b[iv] * c + b[iu] * s);
   }
@@ -129,10 +136,11 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
 
   // key range of this CTA and split
   const int last_row = min(row0 + rows_cta, R) - 1;
-  const int n_keys = pos0 + last_row / hpg + 1;                     // keys 0 .. n_keys-1 are visible to some row of the CTA
-  int per = (n_keys + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int n_keys = pos0 + last_row / hpg + 1;                     // keys k_first .. n_keys-1 are visible to some row of the CTA
+  const int k_first = a.window > 0 ? max(0, pos0 + row0 / hpg - a.window + 1) : 0;
+  int per = (n_keys - k_first + (int)gridDim.y - 1) / (int)gridDim.y;
   per = (per + LAT_BN - 1) / LAT_BN * LAT_BN;
-  const int j_begin = min(n_keys, (int)blockIdx.y * per), j_end = min(n_keys, j_begin + per);
+  const int j_begin = min(n_keys, k_first + (int)blockIdx.y * per), j_end = min(n_keys, j_begin + per);
 
   int lim[LAT_RW];                                                  // last visible key of each row (-1: no such row)
   float m[LAT_RW], l[LAT_RW], acc[LAT_RW][VI];
@@ -146,6 +154,13 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
     for (int i = 0; i < VI; ++i) acc[r][i] = 0.f;
   }
   const int warp_lim = max(max(lim[0], lim[1]), max(lim[2], lim[3]));
+  int first[LAT_RW];                                                // first visible key of each row
+#pragma unroll
+  for (int r = 0; r < LAT_RW; ++r) first[r] = (a.window > 0 && lim[r] >= 0) ? max(0, lim[r] - a.window + 1) : 0;
+  int warp_first = INT_MAX;                                         // of the warp's rows that exist
+#pragma unroll
+  for (int r = 0; r < LAT_RW; ++r)
+    if (lim[r] >= 0) warp_first = min(warp_first, first[r]);
   const int wq = min(warp, row_warps - 1);                          // loader-only warps never read these
   const float* qw = qs + (size_t)wq * LAT_RW * Qp;
   float* pw = ps + (size_t)wq * LAT_RW * LAT_BN;
@@ -185,7 +200,7 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
       }
     }
     __syncthreads();
-    if (jt > warp_lim) continue;                                    // every key of the tile lies after this warp's rows
+    if (jt > warp_lim || jt + LAT_BN <= warp_first) continue;       // every key of the tile lies after or before this warp's rows
     float s[LAT_RW] = {0.f, 0.f, 0.f, 0.f}, s2[LAT_RW] = {0.f, 0.f, 0.f, 0.f};     // two chains per row: the FMAs of one hide the other's latency
     int d = s0;
     for (; d + 8 <= Kp; d += 8) {
@@ -214,7 +229,7 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
     const int j = jt + lane;
 #pragma unroll
     for (int r = 0; r < LAT_RW; ++r) {
-      const bool seen = lane < nk && j <= lim[r];
+      const bool seen = lane < nk && j <= lim[r] && j >= first[r];
       const float sc = seen ? s[r] * a.scale : -INFINITY;
       const float mn = fmaxf(m[r], warp_max(sc));
       float p = 0.f, corr = 1.f;
@@ -256,10 +271,10 @@ __global__ void __launch_bounds__(LAT_THREADS, VI <= 4 ? 3 : 1) seq_latent_atten
     if (row >= R) continue;
     const int t = row / hpg, h = group * hpg + row % hpg;
     if (gridDim.y == 1) {
-      const float sink = a.sink[h];
+      const float sink = a.sink ? a.sink[h] : -INFINITY;            // without a sink every row sees its own key: m is finite
       const float M = fmaxf(m[r], sink);
       const float e = expf(m[r] - M);                               // m = -inf (no key): 0
-      const float inv = e / (l[r] * e + expf(sink - M));
+      const float inv = e / (l[r] * e + (a.sink ? expf(sink - M) : 0.f));
       act_t* o = reinterpret_cast<act_t*>(a.out) + (size_t)t * a.ldo + (size_t)h * a.vdim;
 #pragma unroll
       for (int i = 0; i < VI; ++i) {
@@ -294,7 +309,7 @@ __global__ void __launch_bounds__(256) seq_latent_combine_kernel(const float* __
   const size_t sstep = (size_t)R * stride;
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
-    const float sk = sink[h];
+    const float sk = sink ? sink[h] : -INFINITY;
     float M = sk;
     for (int s = lane; s < splits; s += 32) M = fmaxf(M, w0[(size_t)s * sstep]);
     M = warp_max(M);
@@ -305,7 +320,7 @@ __global__ void __launch_bounds__(256) seq_latent_combine_kernel(const float* __
       comb_f[s] = f;
       den += f * w0[(size_t)s * sstep + 1];
     }
-    den = warp_sum(den) + expf(sk - M);
+    den = warp_sum(den) + (sink ? expf(sk - M) : 0.f);
     const float inv = 1.0f / den;
     for (int s = lane; s < splits; s += 32) comb_f[s] *= inv;
   }
@@ -340,7 +355,7 @@ static int launch_latent(const b2l_seq_latent_attn_args& a, int row_warps, size_
 using namespace b2l;
 
 extern "C" int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* freq, int rot_dims, int interleaved, int rot_off,
-                            float mult, const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size,
+                            float mult, float rot_mult, const int* meta, void* out, int ldo, int out_f32, int T, int heads, int size,
                             int hsx, int hso, int act_dtype, b2l_stream_t stream) {
   B2L_CHECK_ARG(x && meta && out, "b2l_seq_rope: null pointer");
   B2L_CHECK_ARG(T >= 0 && heads > 0 && size > 0 && hsx >= size && hso >= size && ldx >= (heads - 1) * hsx + size && ldo >= (heads - 1) * hso + size,
@@ -351,7 +366,7 @@ extern "C" int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* fre
   const int ids = T * heads, grid = (ids + 3) / 4;
   cudaStream_t st = (cudaStream_t)stream;
 #define B2L_ROPE_GO(IN, OUT) \
-  seq_rope_kernel<IN, OUT><<<grid, 128, 0, st>>>((const IN*)x, ldx, freq, rot_dims, interleaved, rot_off, mult, meta, (OUT*)out, ldo, T, heads, size, hsx, hso)
+  seq_rope_kernel<IN, OUT><<<grid, 128, 0, st>>>((const IN*)x, ldx, freq, rot_dims, interleaved, rot_off, mult, rot_mult, meta, (OUT*)out, ldo, T, heads, size, hsx, hso)
   B2L_SEQ_DISPATCH(act_dtype, {
     if (in_f32 && out_f32) B2L_ROPE_GO(float, float);
     else if (in_f32) B2L_ROPE_GO(float, act_t);
@@ -365,7 +380,7 @@ extern "C" int b2l_seq_rope(const void* x, int ldx, int in_f32, const float* fre
 
 extern "C" int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_rank, const void* w_q, void* cq, int kv_off,
                                    int rank, const void* w_kv, int rot_dim, const float* freq, int rot_dims, int interleaved,
-                                   float eps, const int* meta, void* cache, int max_pos, int T, int act_dtype,
+                                   float rot_mult, float eps, const int* meta, void* cache, int max_pos, int T, int act_dtype,
                                    b2l_stream_t stream) {
   B2L_CHECK_ARG(proj && w_q && cq && w_kv && meta && cache, "b2l_seq_latent_prep: null pointer");
   B2L_CHECK_ARG(T >= 0 && q_rank > 0 && rank > 0 && rot_dim >= 0 && max_pos > 0 && q_off >= 0 && kv_off >= 0 && ld >= q_off + q_rank &&
@@ -374,7 +389,7 @@ extern "C" int b2l_seq_latent_prep(const float* proj, int ld, int q_off, int q_r
   if (T == 0) return 0;
   B2L_SEQ_DISPATCH(act_dtype, {
     seq_latent_prep_kernel<act_t><<<T, 128, 0, (cudaStream_t)stream>>>(proj, ld, q_off, q_rank, (const act_t*)w_q, (act_t*)cq, kv_off, rank,
-                                                                      (const act_t*)w_kv, rot_dim, freq, rot_dims, interleaved, eps, meta,
+                                                                      (const act_t*)w_kv, rot_dim, freq, rot_dims, interleaved, rot_mult, eps, meta,
                                                                       (act_t*)cache, max_pos);
   });
   B2L_LAUNCH_CHECK("seq_latent_prep_kernel");
@@ -389,7 +404,8 @@ extern "C" int b2l_seq_latent_attention_warps(int T, int heads_per_group) {
 
 extern "C" int b2l_seq_latent_attention(const b2l_seq_latent_attn_args* a, b2l_stream_t stream) {
   B2L_CHECK_ARG(a != nullptr, "b2l_seq_latent_attention: null args");
-  B2L_CHECK_ARG(a->q_a && a->key_a && a->sink && a->meta && a->out && (a->n_b == 0 || (a->q_b && a->key_b)), "b2l_seq_latent_attention: null pointer");
+  B2L_CHECK_ARG(a->q_a && a->key_a && a->meta && a->out && (a->n_b == 0 || (a->q_b && a->key_b)), "b2l_seq_latent_attention: null pointer");
+  B2L_CHECK_ARG(a->window >= 0, "b2l_seq_latent_attention: negative window");
   B2L_CHECK_ARG(a->T >= 0 && a->heads > 0 && a->heads_per_group > 0 && a->heads % a->heads_per_group == 0 && a->n_a > 0 && a->n_b >= 0 &&
                     a->vdim > 0 && a->vdim <= a->n_a && a->score_off >= 0 && a->score_off < a->n_a + a->n_b && a->score_off <= a->n_a &&
                     a->splits >= 1 && a->ldo >= a->heads * a->vdim, "b2l_seq_latent_attention: bad size");

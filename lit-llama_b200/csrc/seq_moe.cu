@@ -29,7 +29,7 @@ __device__ __forceinline__ Best warp_best(Best x) {
 // The router of one token by one warp, from its logits zr[n] (global or shared).  s[n] (scores), c[n] (choice
 // scores) and g[groups] are the warp's shared scratch.
 __device__ __forceinline__ void route_token(const float* zr, const float* __restrict__ corr, int n, int groups, int keep, int top,
-                                            int score_fn, int renorm, int* __restrict__ idx_t, float* __restrict__ wgt_t, float* s, float* c,
+                                            int score_fn, int renorm, int group_top, float weight_scale, int* __restrict__ idx_t, float* __restrict__ wgt_t, float* s, float* c,
                                             float* g, int lane) {
   if (score_fn == B2L_SEQ_SCORE_SIGMOID) {
     for (int i = lane; i < n; i += 32) {
@@ -56,9 +56,27 @@ __device__ __forceinline__ void route_token(const float* zr, const float* __rest
   if (groups > 1 && keep < groups) {
     const int per = n / groups;
     for (int q = lane; q < groups; q += 32) {
-      float b = -INFINITY;
-      for (int i = 0; i < per; ++i) b = fmaxf(b, c[q * per + i]);
-      g[q] = b;
+      if (group_top <= 1) {                           // a group is worth its largest choice score
+        float b = -INFINITY;
+        for (int i = 0; i < per; ++i) b = fmaxf(b, c[q * per + i]);
+        g[q] = b;
+      } else {                                        // ... or the sum of its group_top largest: pick them one by one
+        float sum = 0.f, last = INFINITY;
+        int last_i = -1;
+        for (int k = 0; k < group_top && k < per; ++k) {
+          float b = -INFINITY;
+          int bi = -1;
+          for (int i = 0; i < per; ++i) {
+            const float v = c[q * per + i];
+            const bool after = v < last || (v == last && i > last_i);       // not yet picked, in the order (value down, index up)
+            if (after && (bi < 0 || v > b)) { b = v; bi = i; }
+          }
+          sum += b;
+          last = b;
+          last_i = bi;
+        }
+        g[q] = sum;
+      }
     }
     __syncwarp();
     for (int k = 0; k < keep; ++k) {                // the best `keep` groups get the mark +inf
@@ -87,18 +105,18 @@ __device__ __forceinline__ void route_token(const float* zr, const float* __rest
     total += s[e];
     __syncwarp();
   }
-  for (int k = lane; k < top; k += 32) wgt_t[k] = renorm ? s[idx_t[k]] / (total + 1e-20f) : s[idx_t[k]];
+  for (int k = lane; k < top; k += 32) wgt_t[k] = (renorm ? s[idx_t[k]] / (total + 1e-20f) : s[idx_t[k]]) * weight_scale;
 }
 
 // One warp per token.  Shared per warp: s[n], c[n], g[groups].
 __global__ void seq_moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int n, int groups, int keep,
-                                     int top, int score_fn, int renorm, int* __restrict__ idx, float* __restrict__ wgt, int T) {
+                                     int top, int score_fn, int renorm, int group_top, float weight_scale, int* __restrict__ idx, float* __restrict__ wgt, int T) {
   extern __shared__ float route_smem[];
   const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * wpc + warp;
   if (t >= T) return;
   float* s = route_smem + (size_t)warp * (2 * n + groups);
-  route_token(z + (size_t)t * ldz, corr, n, groups, keep, top, score_fn, renorm, idx + (size_t)t * top, wgt + (size_t)t * top, s, s + n, s + 2 * n,
+  route_token(z + (size_t)t * ldz, corr, n, groups, keep, top, score_fn, renorm, group_top, weight_scale, idx + (size_t)t * top, wgt + (size_t)t * top, s, s + n, s + 2 * n,
               lane);
 }
 
@@ -135,8 +153,8 @@ __device__ __forceinline__ float row_dot(const act_t* __restrict__ w, const floa
 template <typename act_t>
 __global__ void __launch_bounds__(1024) seq_moe_route_fused_kernel(const act_t* __restrict__ h, int ldh, const act_t* __restrict__ wr,
                                                                   const float* __restrict__ corr, int D, int n, int groups, int keep, int top,
-                                                                  int score_fn, int renorm, int* __restrict__ idx, float* __restrict__ wgt,
-                                                                  int vec) {
+                                                                  int score_fn, int renorm, int group_top, float weight_scale,
+                                                                  int* __restrict__ idx, float* __restrict__ wgt, int vec) {
   extern __shared__ float route_smem[];
   float* x = route_smem;
   float* z = x + D;
@@ -149,7 +167,7 @@ __global__ void __launch_bounds__(1024) seq_moe_route_fused_kernel(const act_t* 
   }
   __syncthreads();
   if (warp == 0)
-    route_token(z, corr, n, groups, keep, top, score_fn, renorm, idx + (size_t)t * top, wgt + (size_t)t * top, z + n, z + 2 * n, z + 3 * n, lane);
+    route_token(z, corr, n, groups, keep, top, score_fn, renorm, group_top, weight_scale, idx + (size_t)t * top, wgt + (size_t)t * top, z + n, z + 2 * n, z + 3 * n, lane);
 }
 
 // mid[a, j] = gated(W_gate[e] x, W_up[e] x) for assignment a = t * top + k, e = idx[a], x = h_t or (in_scale given) the
@@ -291,8 +309,9 @@ static DynSmemCache g_moe_smem[4];
 using namespace b2l;
 
 extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* correction, int n, int groups, int keep, int top, int score_fn,
-                                 int renormalize, int* idx, float* weights, int T, b2l_stream_t stream) {
+                                 int renormalize, int group_top, float weight_scale, int* idx, float* weights, int T, b2l_stream_t stream) {
   B2L_CHECK_ARG(logits && idx && weights, "b2l_seq_moe_route: null pointer");
+  B2L_CHECK_ARG(group_top >= 1, "b2l_seq_moe_route: a group's score needs at least its largest member");
   B2L_CHECK_ARG(T >= 0 && n > 0 && ld >= n && top > 0 && top <= n && groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups,
                 "b2l_seq_moe_route: bad size");
   B2L_CHECK_ARG((long long)keep * (n / groups) >= top, "b2l_seq_moe_route: the kept groups hold fewer than `top` experts");
@@ -301,8 +320,8 @@ extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* corre
   const int wpc = 4;
   const size_t smem = sizeof(float) * wpc * (2 * (size_t)n + groups);
   B2L_CHECK_SUPPORTED(smem <= 48 * 1024, "b2l_seq_moe_route: %d experts need %zu bytes of shared memory", n, smem);
-  seq_moe_route_kernel<<<(T + wpc - 1) / wpc, wpc * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, groups, keep, top, score_fn, renormalize, idx,
-                                                                                          weights, T);
+  seq_moe_route_kernel<<<(T + wpc - 1) / wpc, wpc * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, groups, keep, top, score_fn, renormalize,
+                                                                                          group_top, weight_scale, idx, weights, T);
   B2L_LAUNCH_CHECK("seq_moe_route_kernel");
   return 0;
 }
@@ -310,9 +329,10 @@ extern "C" int b2l_seq_moe_route(const float* logits, int ld, const float* corre
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_router, const float* correction, int D, int n, int groups,
-                                       int keep, int top, int score_fn, int renormalize, int* idx, float* weights, int T, int act_dtype,
-                                       b2l_stream_t stream) {
+                                       int keep, int top, int score_fn, int renormalize, int group_top, float weight_scale, int* idx,
+                                       float* weights, int T, int act_dtype, b2l_stream_t stream) {
   B2L_CHECK_ARG(h && w_router && idx && weights, "b2l_seq_moe_route_fused: null pointer");
+  B2L_CHECK_ARG(group_top >= 1, "b2l_seq_moe_route_fused: a group's score needs at least its largest member");
   B2L_CHECK_ARG(T >= 0 && D > 0 && ldh >= D && n > 0 && top > 0 && top <= n && groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups,
                 "b2l_seq_moe_route_fused: bad size");
   B2L_CHECK_ARG((long long)keep * (n / groups) >= top, "b2l_seq_moe_route_fused: the kept groups hold fewer than `top` experts");
@@ -327,7 +347,7 @@ extern "C" int b2l_seq_moe_route_fused(const void* h, int ldh, const void* w_rou
     const int rc = ensure_dyn_smem(seq_moe_route_fused_kernel<act_t>, smem, cache[sizeof(act_t) == 2 ? 0 : 1]);
     if (rc != 0) return rc;
     seq_moe_route_fused_kernel<act_t><<<T, n >= 32 ? 1024 : 32 * ((n + 3) / 4 * 4 > 8 ? (n + 3) / 4 * 4 : 8), smem, (cudaStream_t)stream>>>((const act_t*)h, ldh, (const act_t*)w_router, correction, D, n, groups,
-                                                                             keep, top, score_fn, renormalize, idx, weights, vec);
+                                                                             keep, top, score_fn, renormalize, group_top, weight_scale, idx, weights, vec);
   });
   B2L_LAUNCH_CHECK("seq_moe_route_fused_kernel");
   return 0;

@@ -18,6 +18,12 @@ constants are constructor parameters.
                          gate per output channel, ring cache of `window` positions
     PairHashEmbedding    token embedding plus a hashed (previous token, token) embedding, into several residual streams
     HyperConnection      one sublayer's read weights, stream-mixing matrix and write weights over several residual streams
+    DenseMLP             W_down act(W_up h) without a gate: gelu_tanh, silu, or xIELU with its two learned numbers
+    DifferentialAttention  causal softmax attention with two score maps per head over the same values, combined as
+                         a0 - lambda a1 and divided by its root mean square; biases and short convolutions on q / k / v,
+                         interleaved rotation, grouped kv heads, keys and values of its own or of an earlier layer
+    MinGRUMixer          S_t = (1 - z_t) S_(t-1) + z_t c_t per channel with gates that read only the current token, silu gate
+    DepthAverage         the residual step of layers whose input is a learned average over all earlier layers' results
 
 A mixer is built from a dict of weight tensors (`from_weights`) and runs one portion of one sequence:
 `forward(h, ctx)` with h [T, width] in the model's activation dtype.  Products go through torch (cuBLAS), as the
@@ -107,6 +113,32 @@ class GatedMLP:
         S.check(S.lib().b2l_seq_gated_act(_p(gu), 2 * self.ff, _p(mid), ctx.T, self.ff, self.act, self.limit, ctx.act, ctx.stream),
                 "b2l_seq_gated_act")
         return linear(mid, self.w_down)
+
+
+class DenseMLP:
+    """W_down act(W_up h), no gate.  act: gelu_tanh, silu, sigmoid, or xIELU with its two learned numbers `params` = (p, q):
+    softplus(p) z^2 + z/2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 otherwise."""
+
+    ACTS = {"gelu_tanh": S.ACT_GELU_TANH, "silu": S.ACT_SILU, "sigmoid": S.ACT_SIGMOID, "xielu": S.ACT_XIELU}
+
+    def __init__(self, up: torch.Tensor, down: torch.Tensor, act: str = "gelu_tanh", params: Optional[torch.Tensor] = None) -> None:
+        if act not in self.ACTS:
+            raise ValueError(f"dense feed-forward: unknown activation {act!r}")
+        self.ff = up.shape[0]
+        self.w_up, self.w_down = up.contiguous(), down.contiguous()
+        self.act = self.ACTS[act]
+        self.params = params.reshape(-1).contiguous() if params is not None else None
+        if self.act == S.ACT_XIELU and (self.params is None or self.params.numel() != 2):
+            raise ValueError("dense feed-forward: xIELU needs its two numbers")
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {}
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        u = linear(h, self.w_up)
+        S.check(S.lib().b2l_seq_unary_act(_p(u), self.ff, _p(u), self.ff, ctx.T, self.ff, self.act, _p(self.params), ctx.act, ctx.stream),
+                "b2l_seq_unary_act")                      # in place: every element is read and written by the same thread
+        return linear(u, self.w_down)
 
 
 # ------------------------------------------------------------------------------------------------ recurrences
@@ -214,6 +246,38 @@ class Mamba2Mixer:
         out = torch.empty((T, self.inner), dtype=h.dtype, device=dev)
         S.check(lib.b2l_seq_group_norm_gate(_p(y), self.inner, _p(self.w_norm), 0, _p(u), self.n_in, S.ACT_SILU, 1, self.eps, 1.0, _p(out),
                                             self.inner, T, self.inner, self.inner // self.parts, ctx.act, ctx.stream), "b2l_seq_group_norm_gate")
+        return linear(out, self.w_o)
+
+
+class MinGRUMixer:
+    """A gated recurrence whose gates read only the current token, channel by channel:
+
+        z = sigmoid(W_z h + b_z);  u = W_x h + b_x;  c = u + 1/2 where u >= 0, sigmoid(u) where u < 0
+        S_t = (1 - z) S_(t-1) + z c;   y = W_o (S_t * silu(W_g h))
+
+    The three projections are one product; everything after it is f32.  State per sequence: S (f32, width), zero at the
+    start.  Long portions run as chunks in parallel (the recurrence is linear in S)."""
+
+    def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, width: int) -> None:
+        self.name, self.width = name, int(width)
+        parts = [W[p + "z"], W[p + "x"], W[p + "g"]]
+        assert all(w.shape[0] == self.width for w in parts) and W[p + "o"].shape[1] == self.width, "minGRU: projections do not fit the width"
+        self.w_in, (self.o_z, self.o_x, self.o_g) = stack_rows(parts)
+        zero = torch.zeros_like(W[p + "z.b"])
+        self.b_in, _ = stack_rows([W[p + "z.b"] if (p + "z.b") in W else zero, W[p + "x.b"] if (p + "x.b") in W else zero, zero])
+        self.w_o = W[p + "o"].contiguous()
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        return {self.name + ".S": StateSpec((self.width,), torch.float32)}
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T = S.lib(), ctx.T
+        proj = F.linear(h, self.w_in, self.b_in)
+        out = torch.empty((T, self.width), dtype=h.dtype, device=h.device)
+        n_chunks = lib.b2l_seq_mingru_chunks(T)
+        work = torch.empty((n_chunks, 2, self.width), dtype=torch.float32, device=h.device) if n_chunks > 1 else None
+        S.check(lib.b2l_seq_mingru(_p(proj), proj.shape[1], self.o_z, self.o_x, self.o_g, _p(ctx.state[self.name + ".S"]), _p(ctx.meta), _p(out),
+                                   self.width, _p(work), n_chunks, T, self.width, ctx.act, ctx.stream), "b2l_seq_mingru")
         return linear(out, self.w_o)
 
 
@@ -448,7 +512,136 @@ class SlidingWindowAttention:
         return linear(att, self.w_o)
 
 
+class DifferentialAttention:
+    """Causal softmax attention with two score maps per head over the same values.
+
+        q = conv(W_q h + b_q) [heads x 2 x dim], k = conv(W_k h + b_k) [kv_heads x 2 x dim], v = conv(W_v h + b_v) [kv_heads x vdim]
+        conv: a causal convolution of `conv` taps over time on every channel (no bias, no activation)
+        q, k: the first rot.dims entries of every map of every head turn by position, pairs (2i, 2i+1) when `interleaved`
+        a_m = softmax_j(q_m . k_m,j * scale) v_j over all j <= i, for the maps m = 0, 1;  query head h reads key/value head
+        h // (heads / kv_heads)
+        o = a_0 - lambda a_1,  lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff  (one number per layer)
+        y = W_o concat_h(o / sqrt(mean(o^2) + eps) * (1 - diff))
+
+    The three projections are one product.  State per sequence: the last conv - 1 projected rows, and every position's
+    rotated keys and convolved values (`max_positions` of them).  With `kv_from` (an earlier DifferentialAttention with the
+    same head counts and rotation) the layer has only queries of its own: it attends over that layer's keys and values, read
+    from that layer's cache and, for the portion's own tokens, from what that layer left in `ctx.shared` in this step."""
+
+    def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, diff: float,
+                 eps: float, conv: int = 0, rot: Optional[dict] = None, max_positions: int = 0, kv_from: Optional["DifferentialAttention"] = None,
+                 interleaved: bool = True) -> None:
+        if max_positions <= 0:
+            raise ValueError("differential attention caches every position: it needs max_positions")
+        self.name, self.H, self.G, self.K, self.V = name, int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.diff, self.eps, self.max_positions, self.interleaved = float(scale), float(diff), eps, int(max_positions), bool(interleaved)
+        if self.H % self.G or self.K % 2:
+            raise ValueError("differential attention: heads must be a multiple of kv_heads, the map size even")
+        self.src = kv_from
+        if kv_from is not None and (kv_from.src is not None or (kv_from.H, kv_from.G, kv_from.K, kv_from.V) != (self.H, self.G, self.K, self.V)):
+            raise ValueError(f"{name}: keys and values must come from a layer with projections of its own and the same head sizes")
+        names = ["q"] if kv_from is not None else ["q", "k", "v"]
+        rows = {"q": self.H * 2 * self.K, "k": self.G * 2 * self.K, "v": self.G * self.V}
+        for n in names:
+            assert W[p + n].shape[0] == rows[n], f"differential attention: projection {n} does not fit the head sizes"
+        assert W[p + "o"].shape[1] == self.H * self.V, "differential attention: output projection does not fit"
+        self.w_in, offs = stack_rows([W[p + n] for n in names])
+        self.b_in, _ = stack_rows([W[p + n + ".b"] if (p + n + ".b") in W else torch.zeros_like(W[p + n][:, 0]) for n in names])
+        self.o_q, self.o_k, self.o_v = offs[0], (offs[1] if len(offs) > 1 else -1), (offs[2] if len(offs) > 2 else -1)
+        self.C = self.w_in.shape[0]
+        self.taps = int(conv) if conv else 1
+        if self.taps > 1:
+            self.w_conv, _ = stack_rows([W[p + n + ".conv"] for n in names])
+            assert self.w_conv.shape == (self.C, self.taps), "differential attention: convolution weights do not fit"
+        else:
+            self.w_conv = torch.ones((self.C, 1), dtype=self.w_in.dtype, device=self.w_in.device)
+        lam = [float((W[p + f"lq{m}"].double() * W[p + f"lk{m}"].double()).sum()) for m in (1, 2)]
+        self.lam = math.exp(lam[0]) - math.exp(lam[1]) + self.diff
+        self.w_o = W[p + "o"].contiguous()
+        self.rot_dims, self.rot_mult, self.freq = 0, 1.0, None
+        if rot and int(rot.get("dims", 0)):
+            self.rot_dims = int(rot["dims"])
+            f, self.rot_mult = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+            self.freq = f.to(self.w_o.device)
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        dt = self.w_o.dtype
+        out = {self.name + ".conv": StateSpec((self.taps - 1, self.C), dt)} if self.taps > 1 else {}
+        if self.src is None:
+            out[self.name + ".k"] = StateSpec((self.max_positions, self.G * 2 * self.K), dt, zero_on_acquire=False)
+            out[self.name + ".v"] = StateSpec((self.max_positions, self.G * self.V), dt, zero_on_acquire=False)
+        return out
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        lib, T, dev, H, G, K, V = S.lib(), ctx.T, h.device, self.H, self.G, self.K, self.V
+        proj = F.linear(h, self.w_in, self.b_in)
+        q = torch.empty((T, H * 2 * K), dtype=torch.float32, device=dev)
+        own = self.src is None
+        kn = torch.empty((T, G * 2 * K), dtype=proj.dtype, device=dev) if own else None
+        vn = torch.empty((T, G * V), dtype=proj.dtype, device=dev) if own else None
+        a = S.ConvRopeArgs(proj=_p(proj), ld=proj.shape[1], c_off=0, C=self.C, taps=self.taps, w=_p(self.w_conv),
+                           state=_p(ctx.state[self.name + ".conv"]) if self.taps > 1 else None, meta=_p(ctx.meta), q_off=self.o_q, q_heads=2 * H,
+                           k_off=self.o_k, k_heads=2 * G, K=K, v_off=self.o_v, n_v=G * V, freq=_p(self.freq), rot_dims=self.rot_dims,
+                           interleaved=int(self.interleaved), rot_mult=self.rot_mult, q_out=_p(q), k_out=_p(kn), v_out=_p(vn), T=T, act_dtype=ctx.act)
+        S.check(lib.b2l_seq_conv_rope(C.byref(a), ctx.stream), "b2l_seq_conv_rope")
+        if own:
+            ctx.shared["kv:" + self.name] = (kn, vn)
+            holder = self.name
+        else:
+            if ("kv:" + self.src.name) not in ctx.shared:
+                raise RuntimeError(f"{self.name}: layer {self.src.name} has not run in this step")
+            kn, vn = ctx.shared["kv:" + self.src.name]
+            holder = self.src.name
+        maps = torch.empty((T, H * 2 * V), dtype=torch.float32, device=dev)
+        b = S.AttnArgs(q=_p(q), k_new=_p(kn), v_new=_p(vn), ldv=G * V, cache_k=_p(ctx.state[holder + ".k"]), cache_v=_p(ctx.state[holder + ".v"]),
+                       meta=_p(ctx.meta), gate=None, ldg=0, out=_p(maps), ldo=H * 2 * V, scale=self.scale, softcap=0.0, out_mult=1.0, has_sink=0,
+                       block=self.max_positions, T=T, heads=2 * H, kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=0, gate_per_channel=0, maps=2,
+                       out_f32=1, no_append=int(not own))
+        local_attention(b, ctx)
+        y = torch.empty((T, H * V), dtype=h.dtype, device=dev)
+        S.check(lib.b2l_seq_diff_combine(_p(maps), H * 2 * V, self.lam, self.eps, 1.0 - self.diff, _p(y), H * V, T, H, V, ctx.act, ctx.stream),
+                "b2l_seq_diff_combine")
+        return linear(y, self.w_o)
+
+
 # ------------------------------------------------------------------------------------------------ residual streams
+def norm_rows(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], kind: str, eps: float, ctx: StepContext,
+              rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+    """RMS norm ("rms") or layer norm with a bias ("layer") of rows of the f32 stream x [T, width] -> act [n_rows, width]."""
+    n = x.shape[0] if n_rows is None else n_rows
+    out = torch.empty((n, x.shape[1]), dtype=ctx.dtype, device=x.device)
+    S.check(S.lib().b2l_seq_norm(_p(x), _p(w), _p(b), DepthAverage.NORMS[kind], eps, _p(out), _p(rows), n, x.shape[1], ctx.act, ctx.stream), "b2l_seq_norm")
+    return out
+
+
+class DepthAverage:
+    """The residual stream of layers that read a learned average over everything before them.  With X_0 the embedding
+    output and X_(i+1) = x_i + (what layer i's sublayers add to their input x_i), the next layer's input is
+    x_(i+1) = sum_(j <= i+1) avg_i[j] X_j (avg_i None: X_(i+1) itself, the ordinary residual stream).  `history` holds the
+    X_j of one portion ([layers + 1, T, width] f32); `step` writes X_(i+1), forms x_(i+1) and the next norm in one launch."""
+
+    NORMS = {"rms": S.NORM_RMS, "layer": S.NORM_LAYER}
+
+    def __init__(self, weights: List[Optional[torch.Tensor]]) -> None:
+        self.avg = []
+        for i, w in enumerate(weights):
+            if w is not None and w.numel() != i + 2:
+                raise ValueError(f"layer {i}: {w.numel()} depth weights, {i + 2} earlier results")
+            self.avg.append(w.to(torch.float32).contiguous() if w is not None else None)
+
+    def history(self, ctx: StepContext, width: int, device) -> torch.Tensor:
+        return torch.empty((len(self.avg) + 1, ctx.T, width), dtype=torch.float32, device=device)
+
+    def step(self, i: int, hist: torch.Tensor, x_in: torch.Tensor, x_out: torch.Tensor, y1: torch.Tensor, y2: Optional[torch.Tensor], ctx: StepContext, *,
+             norm: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, kind: str = "layer", eps: float = 0.0) -> Optional[torch.Tensor]:
+        """Layer i's results y1 (+ y2) on its input x_in -> the next input in x_out (may be x_in), and its norm (act) when `norm` is given."""
+        T, D = x_in.shape
+        h = torch.empty((T, D), dtype=ctx.dtype, device=x_in.device) if norm is not None else None
+        S.check(S.lib().b2l_seq_depth_step(_p(y1), _p(y2), _p(x_in), _p(hist), i + 2, _p(self.avg[i]), _p(x_out), _p(norm), _p(bias), self.NORMS[kind],
+                                           eps, _p(h), T, D, ctx.act, ctx.stream), "b2l_seq_depth_step")
+        return h
+
+
 class PairHashEmbedding:
     """x = embed[token] * scale + pair[(previous token * mul_prev + token * mul_cur) mod buckets], the first token of a
     sequence reading the pair table's last row (number `buckets`); written into `streams` equal residual streams
@@ -518,6 +711,10 @@ class LatentAttention:
         key_h = [W_uk,h c | k_r],  value_h = W_uv,h c,  score = q . key * scale
         weights exp(s_j) / (exp(sink_h) + sum_j exp(s_j)),  y = W_o concat_h(sum_j weight_j value_j)
 
+    over every earlier position, or with `window` over the query's own position and the window - 1 before it; without a
+    `sink` tensor the softmax is the ordinary one.  A YaRN `scaling` of the rotation stretches the slow frequencies and
+    multiplies cos and sin of q_r and k_r; `scale` is taken as given.
+
     Only [c | k_r] is cached per position.  Single tokens and short portions attend in the latent space: the query is
     multiplied by W_uk once (q' = W_uk,h^T q_h), scores are q' . c + q_r . k_r, the weighted sum of latents is mapped
     through W_uv afterwards; every head reads the same cached row, once.  Portions of `expand_from` tokens or more
@@ -529,9 +726,13 @@ class LatentAttention:
     expand_limit: int = 1 << 31           # ... unless the expansion would have more elements than this
 
     def __init__(self, name: str, W: Dict[str, torch.Tensor], p: str, *, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int,
-                 kv_rank: int, scale: float, eps: float, rot: Optional[dict], max_positions: int, interleaved: bool = True) -> None:
+                 kv_rank: int, scale: float, eps: float, rot: Optional[dict], max_positions: int, interleaved: bool = True,
+                 window: Optional[int] = None) -> None:
         if max_positions <= 0:
             raise ValueError("latent attention caches every position: it needs max_positions")
+        self.window = int(window) if window else 0
+        if self.window < 0:
+            raise ValueError("latent attention: negative window")
         self.name, self.H, self.dn, self.dr, self.dv, self.rq, self.rk = name, heads, dim, rot_dim, vdim, q_rank, kv_rank
         self.scale, self.eps, self.max_positions, self.interleaved = float(scale), eps, int(max_positions), bool(interleaved)
         self.w_in, (self.o_q, self.o_kv) = stack_rows([W[p + "dq"], W[p + "dkv"]])
@@ -543,12 +744,14 @@ class LatentAttention:
         self.w_uk = uk.contiguous()                                                            # q' = q_h W_uk,h
         self.w_uv_t = uv.transpose(1, 2).contiguous()                                          # value = o' W_uv,h^T
         self.w_expand = torch.cat([uv, uk], dim=1).reshape(heads * (vdim + dim), kv_rank).contiguous()   # per head [value | key] rows
-        self.sink = W[p + "sink"].to(torch.float32).contiguous()
+        self.sink = W[p + "sink"].to(torch.float32).contiguous() if (p + "sink") in W else None
         self.w_o = W[p + "o"].contiguous()
-        self.rot_dims, self.freq = 0, None
+        self.rot_dims, self.rot_mult, self.freq = 0, 1.0, None
         if rot and rot_dim:
             self.rot_dims = int(rot["dims"])
-            f, _ = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
+            if self.rot_dims > rot_dim:
+                raise ValueError(f"latent attention: {self.rot_dims} rotated entries in a part of {rot_dim}")
+            f, self.rot_mult = rope_frequencies(self.rot_dims, float(rot["base"]), rot.get("scaling"))
             self.freq = f.to(self.w_o.device)
 
     def state_specs(self) -> Dict[str, StateSpec]:
@@ -558,6 +761,8 @@ class LatentAttention:
         """Key splits: fill the machine when there are few rows; never a function of the position inside a captured step."""
         T = ctx.T
         n_keys = self.max_positions if ctx.pos_hint is None else min(self.max_positions, ctx.pos_hint + T)
+        if self.window:
+            n_keys = min(n_keys, self.window + 4 * S.lib().b2l_seq_latent_attention_warps(T, hpg) // hpg)     # what one CTA's rows see
         warps = S.lib().b2l_seq_latent_attention_warps(T, hpg)
         ctas = -(-T * hpg // (4 * warps)) * (self.H // hpg)
         if ctas >= 444:                       # a full wave of three CTAs per SM
@@ -567,7 +772,7 @@ class LatentAttention:
     def _attend(self, ctx: StepContext, out: torch.Tensor, vdim: int, splits: int, **kw) -> None:
         work = torch.empty((splits, ctx.T * self.H, vdim + 2), dtype=torch.float32, device=out.device) if splits > 1 else None
         a = S.LatentAttnArgs(sink=_p(self.sink), meta=_p(ctx.meta), out=_p(out), ldo=self.H * vdim, work=_p(work), scale=self.scale, T=ctx.T,
-                             heads=self.H, vdim=vdim, splits=splits, act_dtype=ctx.act, **kw)
+                             heads=self.H, vdim=vdim, splits=splits, act_dtype=ctx.act, window=self.window, **kw)
         S.check(S.lib().b2l_seq_latent_attention(C.byref(a), ctx.stream), "b2l_seq_latent_attention")
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
@@ -577,7 +782,7 @@ class LatentAttention:
         cache = ctx.state[self.name + ".kv"]
         Kd = self.rk + self.dr
         S.check(lib.b2l_seq_latent_prep(_p(proj), proj.shape[1], self.o_q, self.rq, _p(self.q_norm), _p(cq), self.o_kv, self.rk, _p(self.kv_norm),
-                                        self.dr, _p(self.freq), self.rot_dims, int(self.interleaved), self.eps, _p(ctx.meta), _p(cache),
+                                        self.dr, _p(self.freq), self.rot_dims, int(self.interleaved), self.rot_mult, self.eps, _p(ctx.meta), _p(cache),
                                         self.max_positions, T, ctx.act, ctx.stream), "b2l_seq_latent_prep")
         dq, f32 = self.dn + self.dr, h.dtype == torch.float32
         q = linear(cq, self.w_uq)                                                   # [T, H * (dim + rot_dim)]
@@ -586,12 +791,13 @@ class LatentAttention:
         if n_pos is not None and T >= self.expand_from and n_pos * H * (self.dv + self.dn) <= self.expand_limit:
             # expanded form: [value_h | key_h] of positions 0 .. n_pos-1 from the cached latents, one product
             q32 = torch.empty((T, H * dq), dtype=torch.float32, device=dev)
-            S.check(lib.b2l_seq_rope(_p(q), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), self.dn, 1.0, _p(ctx.meta),
+            S.check(lib.b2l_seq_rope(_p(q), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), self.dn, 1.0, self.rot_mult, _p(ctx.meta),
                                      _p(q32), H * dq, 1, T, H, dq, dq, dq, ctx.act, ctx.stream), "b2l_seq_rope")
-            kv = linear(cache[ctx.slot_hint, :n_pos, :self.rk], self.w_expand)       # [n_pos, H * (vdim + dim)]
+            lo = max(0, ctx.pos_hint - self.window + 1) if self.window else 0       # the first position any query of the portion sees
+            kv = linear(cache[ctx.slot_hint, lo:n_pos, :self.rk], self.w_expand)     # [n_pos - lo, H * (vdim + dim)]: row j - lo is position j
             att = torch.empty((T, H * self.dv), dtype=h.dtype, device=dev)
             self._attend(ctx, att, self.dv, self._splits(ctx, 1), q_a=_p(q32), ldqa_t=H * dq, ldqa_h=dq, q_b=_p(q32, self.dn), ldqb_t=H * dq,
-                         ldqb_h=dq, key_a=_p(kv), ldka=H * (self.dv + self.dn), hska=self.dv + self.dn, slot_stride_a=0, n_a=self.dv + self.dn,
+                         ldqb_h=dq, key_a=_p(kv, -lo * H * (self.dv + self.dn)), ldka=H * (self.dv + self.dn), hska=self.dv + self.dn, slot_stride_a=0, n_a=self.dv + self.dn,
                          score_off=self.dv, heads_per_group=1, **shared_b)
             return linear(att, self.w_o)
         # latent form
@@ -599,7 +805,7 @@ class LatentAttention:
         q_lat = torch.bmm(qn, self.w_uk) if f32 else torch.bmm(qn, self.w_uk, out_dtype=torch.float32)     # [H, T, rank] f32
         q_rot = torch.empty((T, H, max(self.dr, 1)), dtype=torch.float32, device=dev)
         if self.dr:
-            S.check(lib.b2l_seq_rope(_p(q, self.dn), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), 0, 1.0, _p(ctx.meta),
+            S.check(lib.b2l_seq_rope(_p(q, self.dn), H * dq, int(f32), _p(self.freq), self.rot_dims, int(self.interleaved), 0, 1.0, self.rot_mult, _p(ctx.meta),
                                      _p(q_rot), H * self.dr, 1, T, H, self.dr, dq, self.dr, ctx.act, ctx.stream), "b2l_seq_rope")
         o_lat = torch.empty((T, H * self.rk), dtype=h.dtype, device=dev)
         self._attend(ctx, o_lat, self.rk, self._splits(ctx, H), q_a=_p(q_lat), ldqa_t=self.rk, ldqa_h=T * self.rk, q_b=_p(q_rot),
@@ -646,7 +852,7 @@ class RetentionMixer:
         qkv = torch.empty((T, 2 * H * K + H * V), dtype=torch.float32, device=dev)
         n = qkv.shape[1]
         for off_in, off_out, mult in ((self.o_q, 0, 1.0), (self.o_k, H * K, K ** -0.5)):
-            S.check(lib.b2l_seq_rope(_p(proj, off_in), ld, f32in, _p(self.freq), self.rot_dims, int(self.interleaved), 0, mult, _p(ctx.meta),
+            S.check(lib.b2l_seq_rope(_p(proj, off_in), ld, f32in, _p(self.freq), self.rot_dims, int(self.interleaved), 0, mult, 1.0, _p(ctx.meta),
                                      _p(qkv, off_out), n, 1, T, H, K, K, K, ctx.act, ctx.stream), "b2l_seq_rope")
         S.check(lib.b2l_seq_cast_f32(_p(proj, self.o_v), ld, _p(qkv, 2 * H * K), n, T, H * V, ctx.act, ctx.stream), "b2l_seq_cast_f32")
         o = torch.empty((T, H * V), dtype=torch.float32, device=dev)
@@ -663,9 +869,10 @@ class MoEFeedForward:
     """y = sum over the chosen experts of weight_e * expert_e(h).
 
         s = softmax(W_router h) over all experts, or sigmoid of each logit (`score`), f32;  choice = s + correction
-        (steers the choice only); experts form `groups` equal groups of neighbours; only experts of the `keep` groups
-        with the largest best choice score can be chosen; the `top` largest choice scores win;
-        weight = s / (sum of the chosen s + 1e-20) when `renormalize`, else s itself
+        (steers the choice only); experts form `groups` equal groups of neighbours; a group is worth the sum of its
+        `group_top` largest choice scores (1: its best); only experts of the `keep` best groups can be chosen; the `top`
+        largest choice scores win;  weight = s / (sum of the chosen s + 1e-20) when `renormalize`, else s itself, times
+        `weight_scale`
         expert e < experts: W_down unit(W_gate x, W_up x) with unit(a, b) = act(a) * b, or the clamped unit
         min(a, limit) * sigmoid(1.702 min(a, limit)) * (clamp(b, -limit, limit) + 1) (`act` = "clamped_swish");
         x = h and the weight scales the expert's output, or (`weight_on` = "input") x = weight * h and the outputs are
@@ -680,7 +887,11 @@ class MoEFeedForward:
     SCORES = {"softmax": S.SCORE_SOFTMAX, "sigmoid": S.SCORE_SIGMOID}
 
     def __init__(self, W: Dict[str, torch.Tensor], p: str, *, experts: int, identity: int, top: int, groups: int, keep: int, ff: int,
-                 act: str = "silu", limit: float = 0.0, score: str = "softmax", renormalize: bool = True, weight_on: str = "output") -> None:
+                 act: str = "silu", limit: float = 0.0, score: str = "softmax", renormalize: bool = True, weight_on: str = "output",
+                 group_top: int = 1, weight_scale: float = 1.0) -> None:
+        self.group_top, self.weight_scale = int(group_top), float(weight_scale)
+        if self.group_top < 1:
+            raise ValueError("routed experts: a group's score needs at least its best member")
         self.E, self.I, self.top, self.groups, self.keep, self.ff = int(experts), int(identity), int(top), int(groups), int(keep), int(ff)
         self.n = self.E + self.I
         if self.n % self.groups or not (1 <= self.keep <= self.groups) or self.keep * (self.n // self.groups) < self.top:
@@ -716,13 +927,14 @@ class MoEFeedForward:
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         if T <= self.SMALL:        # a few tokens: the logits and the routing in one launch
             S.check(lib.b2l_seq_moe_route_fused(_p(h), D, _p(self.w_router), _p(self.correction), D, self.n, self.groups, self.keep, self.top,
-                                                self.score, self.renorm, _p(idx), _p(wgt), T, ctx.act, ctx.stream), "b2l_seq_moe_route_fused")
+                                                self.score, self.renorm, self.group_top, self.weight_scale, _p(idx), _p(wgt), T, ctx.act,
+                                                ctx.stream), "b2l_seq_moe_route_fused")
             self.last_idx = idx
             return idx, wgt
         # f32 logits: bf16 activations and router weights are exact in f32, the product keeps its f32 accumulator
         z = linear_f32(h, self.w_router)
         S.check(lib.b2l_seq_moe_route(_p(z), self.n, _p(self.correction), self.n, self.groups, self.keep, self.top, self.score, self.renorm,
-                                      _p(idx), _p(wgt), T, ctx.stream), "b2l_seq_moe_route")
+                                      self.group_top, self.weight_scale, _p(idx), _p(wgt), T, ctx.stream), "b2l_seq_moe_route")
         self.last_idx = idx
         return idx, wgt
 

@@ -42,6 +42,13 @@ def _load_zuvevik(model_dir: str, dtype: torch.dtype, device: torch.device, max_
     return zuvevik.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
 
 
+@register("Rinirax")
+def _load_rinirax(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
+    from . import rinirax
+
+    return rinirax.load(model_dir, dtype=dtype, device=device, max_positions=max_positions)
+
+
 @register("LLaMA")
 def _load_llama(model_dir: str, dtype: torch.dtype, device: torch.device, max_positions: int, config: dict):
     """config.json: {"architecture": "LLaMA", "name": "7B" | sizes..., "quantize": null | "gptq.int4" | ..., "checkpoint": file}."""

@@ -140,7 +140,8 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
             "device-indexed expert products" if tt <= moe.SMALL else "sort + gather + per-expert library products + combine")
         idx, wgt = moe.route(hh, ctx)
         z = torch.randn(tt, moe.n, device=device)
-        t = timer(lambda: S.check(lib.b2l_seq_moe_route(M._p(z), moe.n, M._p(moe.correction), moe.n, moe.groups, moe.keep, moe.top, moe.score, moe.renorm, M._p(idx), M._p(wgt),
+        t = timer(lambda: S.check(lib.b2l_seq_moe_route(M._p(z), moe.n, M._p(moe.correction), moe.n, moe.groups, moe.keep, moe.top, moe.score, moe.renorm, moe.group_top, moe.weight_scale,
+                                                        M._p(idx), M._p(wgt),
                                                         tt, ctx.stream), "k"))
         add("seq_moe_route_kernel", "-", tt, t, tt * (moe.n * 4 + moe.top * 8))
     engine.pool.release("kernels")

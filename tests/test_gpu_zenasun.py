@@ -461,7 +461,7 @@ def test_group_limit_and_negative_choice_scores():
     idx = torch.empty(T, 2, dtype=torch.int32, device=DEV)
     wgt = torch.empty(T, 2, device=DEV)
     zd, cd = z.to(DEV), corr.to(DEV)
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, cd.data_ptr(), n, 4, 3, 2, S.SCORE_SOFTMAX, 1, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, cd.data_ptr(), n, 4, 3, 2, S.SCORE_SOFTMAX, 1, 1, 1.0, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     s = torch.softmax(z.double(), -1)[0]
     choice = s + corr.double()
     assert float(choice[2]) < float(choice.max()) and 2 not in idx.cpu().tolist()[0]
@@ -470,7 +470,7 @@ def test_group_limit_and_negative_choice_scores():
     assert idx.cpu().tolist()[0] == best
     assert torch.allclose(wgt.cpu().double()[0], s[best] / s[best].sum(), rtol=1e-5)
     # with every group kept the same expert wins on its choice score only if the correction lets it
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 4, 4, 2, S.SCORE_SOFTMAX, 1, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 4, 4, 2, S.SCORE_SOFTMAX, 1, 1, 1.0, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     assert idx.cpu().tolist()[0][0] == 2
 
 
@@ -505,7 +505,7 @@ def test_norm_pair_and_softcap_and_rotation():
     for inter in (0, 1):
         out = torch.empty(T, H * size, device=DEV)
         vd = v.to(DEV)
-        S.check(lib.b2l_seq_rope(vd.data_ptr(), H * size, 1, freq.data_ptr(), dims, inter, off, 0.5, meta.data_ptr(), out.data_ptr(), H * size, 1, T, H,
+        S.check(lib.b2l_seq_rope(vd.data_ptr(), H * size, 1, freq.data_ptr(), dims, inter, off, 0.5, 1.0, meta.data_ptr(), out.data_ptr(), H * size, 1, T, H,
                                  size, size, size, S.B2L_F32, None), "rope")
         want = v.double().view(T, H, size).clone()
         for hd in range(H):

@@ -528,11 +528,11 @@ def test_sigmoid_scores_without_renormalisation():
     idx = torch.empty(T, 3, dtype=torch.int32, device=DEV)
     wgt = torch.empty(T, 3, dtype=torch.float32, device=DEV)
     zd = z.to(DEV)
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 1, 1, 3, S.SCORE_SIGMOID, 0, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 1, 1, 3, S.SCORE_SIGMOID, 0, 1, 1.0, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     want = torch.sigmoid(z).topk(3, dim=-1)
     assert idx.cpu().tolist() == want.indices.tolist()
     assert float((wgt.cpu() - want.values).abs().max()) < 1e-6
-    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 1, 1, 3, S.SCORE_SIGMOID, 1, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
+    S.check(S.lib().b2l_seq_moe_route(zd.data_ptr(), n, None, n, 1, 1, 3, S.SCORE_SIGMOID, 1, 1, 1.0, idx.data_ptr(), wgt.data_ptr(), T, None), "route")
     assert float((wgt.cpu() - want.values / want.values.sum(-1, keepdim=True)).abs().max()) < 1e-6
 
 
