@@ -550,10 +550,10 @@ class DifferentialAttention:
         self.o_q, self.o_k, self.o_v = offs[0], (offs[1] if len(offs) > 1 else -1), (offs[2] if len(offs) > 2 else -1)
         self.C = self.w_in.shape[0]
         self.taps = int(conv) if conv else 1
-        if self.taps > 1:
+        if conv:
             self.w_conv, _ = stack_rows([W[p + n + ".conv"] for n in names])
             assert self.w_conv.shape == (self.C, self.taps), "differential attention: convolution weights do not fit"
-        else:
+        else:                                   # no convolution: one tap of weight one
             self.w_conv = torch.ones((self.C, 1), dtype=self.w_in.dtype, device=self.w_in.device)
         lam = [float((W[p + f"lq{m}"].double() * W[p + f"lk{m}"].double()).sum()) for m in (1, 2)]
         self.lam = math.exp(lam[0]) - math.exp(lam[1]) + self.diff
