@@ -387,14 +387,20 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="N > 1: skip the tensor-parallel block")
-    ap.add_argument("--family", default="llama", choices=["llama", "lugovik", "zenasun", "zuvevik"],
+    ap.add_argument("--family", default="llama", choices=["llama", "lugovik", "zenasun", "zuvevik", "rinirax"],
                     help="llama (default): the headline 7B gptq.int4 decode benchmark; lugovik: prefill / decode throughput of the Lugovik "
                          "family beside the dense LLaMA at equal width and depth, with a per-kernel table (1 GPU); zenasun: the same for "
-                         "the Zenasun family beside Lugovik; zuvevik: the same for the Zuvevik family beside Lugovik")
+                         "the Zenasun family beside Lugovik; zuvevik: the same for the Zuvevik family beside Lugovik; rinirax: the same for the "
+                         "Rinirax family beside Zenasun")
     ap.add_argument("--sizes", default="1k,2k", help="--family lugovik / zenasun: comma-separated model sizes (1k, 2k, 4k = width; zenasun: 1k, 2k)")
     ap.add_argument("--prompt", type=int, default=2048, help="--family lugovik / zenasun: prompt length of the prefill measurement")
     ap.add_argument("--decode-steps", type=int, default=64, help="--family lugovik / zenasun: timed single-token steps")
     args = ap.parse_args()
+    if args.family == "rinirax":
+        from lit_llama_b200 import rinirax_bench
+
+        print(json.dumps(rinirax_bench.run(args, [x for x in args.sizes.split(",") if x])), flush=True)
+        return
     if args.family == "zuvevik":
         from lit_llama_b200 import zuvevik_bench
 
