@@ -50,10 +50,10 @@ enum { B2L_SEQ_ACT_GELU_TANH = 0, B2L_SEQ_ACT_SILU = 1, B2L_SEQ_ACT_SIGMOID = 2,
 int b2l_seq_gated_act(const void* gu, int ldgu, void* out, int T, int F, int act, float limit, int act_dtype, b2l_stream_t stream);
 
 /* out[t, j] = act(in[t, j]) for an ungated feed-forward: gelu_tanh, silu, sigmoid, or B2L_SEQ_ACT_XIELU with its two
- * learned numbers params = {p, q} (act, on the device), a = softplus(p), b = 1/2 + softplus(q):
+ * coefficients coef = {a, b} (f32, on the device; from the learned numbers p, q: a = softplus(p), b = 1/2 + softplus(q)):
  *   z > 0: a z^2 + z / 2;   z <= 0: b (exp(z) - 1 - z) + z / 2.
- * `params` is read by xIELU alone. */
-int b2l_seq_unary_act(const void* in, int ldin, void* out, int ldout, int T, int F, int act, const void* params, int act_dtype,
+ * `coef` is read by xIELU alone.  out may be in (in place). */
+int b2l_seq_unary_act(const void* in, int ldin, void* out, int ldout, int T, int F, int act, const float* coef, int act_dtype,
                       b2l_stream_t stream);
 
 /* Short causal convolution over time per channel, then silu, with the last taps-1 inputs of the sequence carried

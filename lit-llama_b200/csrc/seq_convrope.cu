@@ -7,7 +7,7 @@
 
 namespace b2l {
 
-constexpr int CR_TT = 32;            // tokens per tile
+constexpr int CR_TT = 8;             // tokens per tile (at least the most taps - 1: a later tile never reads the carried rows)
 constexpr int CR_MAX_TAPS = 8;
 constexpr int CR_THREADS = 128;
 

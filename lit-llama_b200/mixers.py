@@ -127,16 +127,20 @@ class DenseMLP:
         self.ff = up.shape[0]
         self.w_up, self.w_down = up.contiguous(), down.contiguous()
         self.act = self.ACTS[act]
-        self.params = params.reshape(-1).contiguous() if params is not None else None
-        if self.act == S.ACT_XIELU and (self.params is None or self.params.numel() != 2):
-            raise ValueError("dense feed-forward: xIELU needs its two numbers")
+        self.coef = None
+        if self.act == S.ACT_XIELU:
+            if params is None or params.numel() != 2:
+                raise ValueError("dense feed-forward: xIELU needs its two numbers")
+            pq = params.detach().reshape(-1).double().cpu()
+            sp = torch.nn.functional.softplus(pq)                       # the two coefficients, once, in 64-bit; kept as f32
+            self.coef = torch.stack([sp[0], 0.5 + sp[1]]).to(torch.float32).to(up.device)
 
     def state_specs(self) -> Dict[str, StateSpec]:
         return {}
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         u = linear(h, self.w_up)
-        S.check(S.lib().b2l_seq_unary_act(_p(u), self.ff, _p(u), self.ff, ctx.T, self.ff, self.act, _p(self.params), ctx.act, ctx.stream),
+        S.check(S.lib().b2l_seq_unary_act(_p(u), self.ff, _p(u), self.ff, ctx.T, self.ff, self.act, _p(self.coef), ctx.act, ctx.stream),
                 "b2l_seq_unary_act")                      # in place: every element is read and written by the same thread
         return linear(u, self.w_down)
 

@@ -210,7 +210,7 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
         add("MinGRUMixer whole (2 products + recurrence)", tt, t, wb + 2 * tt * D * es, 2.0 * tt * wb / es)
         # ---- feed-forward
         u = torch.randn(tt, dense.ff, device=device).to(dt)
-        t = timer(lambda: S.check(lib.b2l_seq_unary_act(M._p(u), dense.ff, M._p(u), dense.ff, tt, dense.ff, dense.act, M._p(dense.params), ctx.act, ctx.stream), "k"))
+        t = timer(lambda: S.check(lib.b2l_seq_unary_act(M._p(u), dense.ff, M._p(u), dense.ff, tt, dense.ff, dense.act, M._p(dense.coef), ctx.act, ctx.stream), "k"))
         add("seq_unary_act_kernel (xIELU in place)", tt, t, tt * dense.ff * 2 * es)
         gu = torch.randn(tt, 2 * dense.ff, device=device).to(dt)
         t = timer(lambda: S.check(lib.b2l_seq_gated_act(M._p(gu), 2 * dense.ff, M._p(u), tt, dense.ff, S.ACT_SILU, 0.0, ctx.act, ctx.stream), "k"))

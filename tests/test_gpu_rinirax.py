@@ -584,9 +584,11 @@ def test_depth_step_norm_and_activation_kernels_alone():
     assert rel(out, O.layer_norm(x.double().cpu(), 1.0, 0.0, 1e-6)) < 2e-3
     for F, dtype in ((50, torch.float32), (384, torch.float32), (384, torch.bfloat16)):
         z = (3.0 * torch.randn(7, F, generator=g)).bfloat16().float()
+        z[0, :8] = torch.tensor([0.0, -1e-4, -0.2490, -0.2501, -0.25, 1e-4, -30.0, -100.0])     # both forms of the negative side and their border
         pq = torch.tensor([0.3, -0.6]).bfloat16().float()
-        zd, pqd = z.to(DEV, dtype), pq.to(DEV, dtype)
-        S.check(lib.b2l_seq_unary_act(zd.data_ptr(), F, zd.data_ptr(), F, 7, F, S.ACT_XIELU, pqd.data_ptr(), S.act_code(dtype), None), "act")
+        zd = z.to(DEV, dtype)
+        coef = torch.tensor([O.softplus(float(pq[0])), 0.5 + O.softplus(float(pq[1]))], dtype=torch.float32, device=DEV)
+        S.check(lib.b2l_seq_unary_act(zd.data_ptr(), F, zd.data_ptr(), F, 7, F, S.ACT_XIELU, coef.data_ptr(), S.act_code(dtype), None), "act")
         assert rel(zd, O.xielu(z.double(), float(pq[0]), float(pq[1]))) < (1e-6 if dtype == torch.float32 else 4e-3)
 
 
