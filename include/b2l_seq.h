@@ -166,6 +166,12 @@ typedef struct {
   int out_f32;                    /* out is f32 [T, ldo] instead of act */
   int no_append;                  /* leave the ring as it is: the portion's keys and values are another layer's, which
                                      appends them itself */
+  /* Differential read-out of two maps (maps == 2, out_f32, no gate), when diff_out is given: per real head
+   *   o = a_0 - diff_lambda a_1;   diff_out[t, h*V : (h+1)*V] = o / sqrt(mean(o^2) + diff_eps) * diff_mult   (act [T, ldd])
+   * `out` (f32 [T, ldo]) is then only a scratch for the maps: the few-query form merges both maps of a head in one CTA
+   * and never writes it, the other forms run the read-out as a second kernel of the call. */
+  void* diff_out; int ldd;
+  float diff_lambda, diff_eps, diff_mult;
 } b2l_seq_attn_args;
 int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t stream);
 /* With few queries (decoding) the keys of a query are cut into chunks that run in parallel and are merged afterwards;

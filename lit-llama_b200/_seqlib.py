@@ -48,6 +48,8 @@ class AttnArgs(C.Structure):
         ("window", c_int), ("gate_per_channel", c_int),
         ("work", c_void_p), ("work_floats", c_int),
         ("maps", c_int), ("out_f32", c_int), ("no_append", c_int),
+        ("diff_out", c_void_p), ("ldd", c_int),
+        ("diff_lambda", c_float), ("diff_eps", c_float), ("diff_mult", c_float),
     ]
 
 

@@ -299,13 +299,12 @@ __global__ void __launch_bounds__(DEC_THREADS) seq_attention_chunk_kernel(b2l_se
 // out[t, h] = gate * out_mult * sum_c e^(m_c - M) acc_c / (sink e^(-M) + sum_c e^(m_c - M) l_c): one CTA per (query, head).
 // The chunk factors go through shared memory, so the loads of the channel sums do not wait for one another.
 constexpr int MERGE_THREADS = 128;
-template <typename act_t>
-__global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_seq_attn_args a, int n_chunks) {
-  extern __shared__ float merge_f[];                 // [n_chunks]
-  __shared__ float red[MERGE_THREADS / 32];
-  const int pair = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t = pair / a.heads, h = pair - t * a.heads, V = a.V;
-  const float* part = a.work + (size_t)pair * n_chunks * (V + 2);
+
+// The merged, normalised output channels `ch = tid + 128 i` of one (query, virtual head) row into val[i]; the sink and
+// out_mult are applied, gates are not.  Ends with every thread past its reads of merge_f and red.
+__device__ __forceinline__ void merge_row(const b2l_seq_attn_args& a, const float* __restrict__ part, int n_chunks, float* merge_f, float* red,
+                                          float (&val)[ATT_VMAX * 32 / MERGE_THREADS]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, V = a.V;
   float M = a.has_sink ? 0.f : -INFINITY;
   for (int c = tid; c < n_chunks; c += MERGE_THREADS) M = fmaxf(M, part[(size_t)c * (V + 2)]);
   M = warp_max(M);
@@ -328,11 +327,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_
 #pragma unroll
   for (int w = 0; w < MERGE_THREADS / 32; ++w) l += red[w];
   if (a.has_sink) l += expf(0.f - M);
-  float f = a.out_mult / l;
-  const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
-  if (a.gate && !a.gate_per_channel) f *= sigmoid_f(ld_act(gate, h));
-  const size_t o = (size_t)t * a.ldo + (size_t)h * V;
-  for (int ch = tid; ch < V; ch += MERGE_THREADS) {
+  const float f = a.out_mult / l;
+#pragma unroll
+  for (int i = 0; i < ATT_VMAX * 32 / MERGE_THREADS; ++i) {
+    const int ch = tid + i * MERGE_THREADS;
+    val[i] = 0.f;
+    if (ch >= V) continue;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int c = 0;
     for (; c + 4 <= n_chunks; c += 4) {
@@ -347,8 +347,56 @@ __global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_
       const float fc = merge_f[c];
       if (fc != 0.f) acc[0] = fmaf(part[(size_t)c * (V + 2) + 2 + ch], fc, acc[0]);
     }
-    const float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    st_out<act_t>(a, o + ch, sum * f * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
+    val[i] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * f;
+  }
+  __syncthreads();
+}
+
+// DIFF == false: one CTA per (query, virtual head): merge, gate, store.
+// DIFF == true (two maps per head and a differential read-out asked for): one CTA per (query, real head) merges both maps
+// and stores (a_0 - lambda a_1) / rms * mult in the activation type: the maps never go through memory.
+template <typename act_t, bool DIFF>
+__global__ void __launch_bounds__(MERGE_THREADS) seq_attention_merge_kernel(b2l_seq_attn_args a, int n_chunks) {
+  extern __shared__ float merge_f[];                 // [n_chunks]
+  __shared__ float red[MERGE_THREADS / 32];
+  constexpr int CPT = ATT_VMAX * 32 / MERGE_THREADS;  // channels per thread
+  const int tid = threadIdx.x, V = a.V;
+  if (!DIFF) {
+    const int pair = blockIdx.x, t = pair / a.heads, h = pair - t * a.heads;
+    float val[CPT];
+    merge_row(a, a.work + (size_t)pair * n_chunks * (V + 2), n_chunks, merge_f, red, val);
+    const act_t* gate = (const act_t*)a.gate + (size_t)t * a.ldg;
+    const float g = (a.gate && !a.gate_per_channel) ? sigmoid_f(ld_act(gate, h)) : 1.f;
+    const size_t o = (size_t)t * a.ldo + (size_t)h * V;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int ch = tid + i * MERGE_THREADS;
+      if (ch < V) st_out<act_t>(a, o + ch, val[i] * g * ((a.gate && a.gate_per_channel) ? sigmoid_f(ld_act(gate, (size_t)h * V + ch)) : 1.f));
+    }
+  } else {
+    const int real = a.heads / 2, t = blockIdx.x / real, hr = blockIdx.x - t * real;
+    float v0[CPT], v1[CPT];
+    merge_row(a, a.work + (size_t)(t * a.heads + 2 * hr) * n_chunks * (V + 2), n_chunks, merge_f, red, v0);
+    merge_row(a, a.work + (size_t)(t * a.heads + 2 * hr + 1) * n_chunks * (V + 2), n_chunks, merge_f, red, v1);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      v0[i] -= a.diff_lambda * v1[i];                 // channels beyond V are 0 in both
+      ss += v0[i] * v0[i];
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) ss += red[w];
+    const float r = a.diff_mult / sqrtf(ss / (float)V + a.diff_eps);
+    act_t* o = (act_t*)a.diff_out + (size_t)t * a.ldd + (size_t)hr * V;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int ch = tid + i * MERGE_THREADS;
+      if (ch < V) st_act(o, ch, v0[i] * r);
+    }
   }
 }
 
@@ -655,6 +703,8 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
   B2L_CHECK_ARG(a->maps >= 0 && a->heads % (a->kv_heads * (a->maps > 1 ? a->maps : 1)) == 0,
                 "b2l_seq_block_attention: heads %d not a multiple of kv_heads %d times maps %d", a->heads, a->kv_heads, a->maps);
   B2L_CHECK_ARG(!(a->gate && a->out_f32), "b2l_seq_block_attention: a gated output is stored in the activation type");
+  B2L_CHECK_ARG(a->diff_out == nullptr || (a->maps == 2 && a->out_f32 && !a->gate && a->ldd >= a->heads / 2 * a->V && a->ldo >= a->heads * a->V),
+                "b2l_seq_block_attention: the differential read-out wants two maps per head, f32 maps in `out` and no gate");
   B2L_CHECK_ARG(a->window >= 0 && (a->window == 0 || a->block >= a->window), "b2l_seq_block_attention: a ring of %d positions cannot serve a window of %d",
                 a->block, a->window);
   B2L_CHECK_SUPPORTED(a->V <= ATT_VMAX * 32, "b2l_seq_block_attention: value size %d above %d", a->V, ATT_VMAX * 32);
@@ -679,12 +729,14 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
       int rc = ensure_dyn_smem(seq_attention_chunk_kernel<__nv_bfloat16>, chunk_smem, g_chunk_smem[0]);
       if (rc) return rc;
       seq_attention_chunk_kernel<__nv_bfloat16><<<grid, DEC_THREADS, chunk_smem, s>>>(*a, n_chunks, vec16);
-      seq_attention_merge_kernel<__nv_bfloat16><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+      if (a->diff_out) seq_attention_merge_kernel<__nv_bfloat16, true><<<pairs / 2, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+      else seq_attention_merge_kernel<__nv_bfloat16, false><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
     } else {
       int rc = ensure_dyn_smem(seq_attention_chunk_kernel<float>, chunk_smem, g_chunk_smem[1]);
       if (rc) return rc;
       seq_attention_chunk_kernel<float><<<grid, DEC_THREADS, chunk_smem, s>>>(*a, n_chunks, vec16);
-      seq_attention_merge_kernel<float><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+      if (a->diff_out) seq_attention_merge_kernel<float, true><<<pairs / 2, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
+      else seq_attention_merge_kernel<float, false><<<pairs, MERGE_THREADS, sizeof(float) * n_chunks, s>>>(*a, n_chunks);
     }
     B2L_LAUNCH_CHECK("seq_attention_chunk_kernel");
     if (a->T == 1 || a->no_append) return 0;        // a single token was appended by its first chunk
@@ -719,6 +771,12 @@ extern "C" int b2l_seq_block_attention(const b2l_seq_attn_args* a, b2l_stream_t 
     else seq_block_attention_kernel<float, 1><<<(pairs + 3) / 4, 128, smem, s>>>(*a, vec);
   }
   B2L_LAUNCH_CHECK("seq_block_attention_kernel");
+  if (a->diff_out) {                                  // the read-out of the two maps, from the f32 maps in `out`
+    const int ids = a->T * (a->heads / 2);
+    B2L_SEQ_DISPATCH(a->act_dtype, (seq_diff_combine_kernel<act_t><<<(ids + 3) / 4, 128, 0, s>>>((const float*)a->out, a->ldo, a->diff_lambda, a->diff_eps, a->diff_mult,
+                                                                                                   (act_t*)a->diff_out, a->ldd, a->T, a->heads / 2, a->V)));
+    B2L_LAUNCH_CHECK("seq_diff_combine_kernel");
+  }
   if (a->no_append) return 0;
   const int n_app = std::min(a->T, a->block);
   if (a->act_dtype == B2L_BF16) seq_ring_append_kernel<__nv_bfloat16><<<n_app, 128, 0, s>>>(*a);

@@ -596,15 +596,14 @@ class DifferentialAttention:
                 raise RuntimeError(f"{self.name}: layer {self.src.name} has not run in this step")
             kn, vn = ctx.shared["kv:" + self.src.name]
             holder = self.src.name
-        maps = torch.empty((T, H * 2 * V), dtype=torch.float32, device=dev)
+        maps = torch.empty((T, H * 2 * V), dtype=torch.float32, device=dev)      # scratch of the forms that do not merge the maps themselves
+        y = torch.empty((T, H * V), dtype=h.dtype, device=dev)
         b = S.AttnArgs(q=_p(q), k_new=_p(kn), v_new=_p(vn), ldv=G * V, cache_k=_p(ctx.state[holder + ".k"]), cache_v=_p(ctx.state[holder + ".v"]),
                        meta=_p(ctx.meta), gate=None, ldg=0, out=_p(maps), ldo=H * 2 * V, scale=self.scale, softcap=0.0, out_mult=1.0, has_sink=0,
                        block=self.max_positions, T=T, heads=2 * H, kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=0, gate_per_channel=0, maps=2,
-                       out_f32=1, no_append=int(not own))
-        local_attention(b, ctx)
-        y = torch.empty((T, H * V), dtype=h.dtype, device=dev)
-        S.check(lib.b2l_seq_diff_combine(_p(maps), H * 2 * V, self.lam, self.eps, 1.0 - self.diff, _p(y), H * V, T, H, V, ctx.act, ctx.stream),
-                "b2l_seq_diff_combine")
+                       out_f32=1, no_append=int(not own), diff_out=_p(y), ldd=H * V, diff_lambda=self.lam, diff_eps=self.eps,
+                       diff_mult=1.0 - self.diff)
+        local_attention(b, ctx)                 # attention of both maps and the differential read-out
         return linear(y, self.w_o)
 
 

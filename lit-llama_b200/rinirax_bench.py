@@ -125,18 +125,14 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
         y = torch.empty(tt, H * V, dtype=dt, device=device)
         bA = S.AttnArgs(q=M._p(qr), k_new=M._p(kr), v_new=M._p(vn), ldv=G * V, cache_k=M._p(ck), cache_v=M._p(cv), meta=M._p(meta), gate=None, ldg=0,
                         out=M._p(maps), ldo=H * 2 * V, scale=att.scale, softcap=0.0, out_mult=1.0, has_sink=0, block=att.max_positions, T=tt, heads=2 * H,
-                        kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=0, gate_per_channel=0, maps=2, out_f32=1, no_append=0)
-
-        def diff_attention():
-            M.local_attention(bA, ctx)
-            S.check(lib.b2l_seq_diff_combine(M._p(maps), H * 2 * V, att.lam, eps, 0.5, M._p(y), H * V, tt, H, V, ctx.act, ctx.stream), "k")
-
-        t = timer(diff_attention)
+                        kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=0, gate_per_channel=0, maps=2, out_f32=1, no_append=0, diff_out=M._p(y), ldd=H * V,
+                        diff_lambda=att.lam, diff_eps=eps, diff_mult=0.5)
+        t = timer(lambda: M.local_attention(bA, ctx))
         nb = tt * (H * 2 * K * 4 + G * (2 * K + V) * es * 2 + H * V * es) + (keys * G * (2 * K + V) * es if tt == 1 else 0)
-        add("seq_block_attention (2 maps per head, f32 maps) + seq_diff_combine + append", tt, t, nb, 2.0 * tt * 2 * H * keys * (K + V),
+        add("seq_block_attention (2 maps per head + differential read-out) + append", tt, t, nb, 2.0 * tt * 2 * H * keys * (K + V),
             f"f32 scores on CUDA cores, {keys:.0f} keys per query")
         t = timer(lambda: S.check(lib.b2l_seq_diff_combine(M._p(maps), H * 2 * V, att.lam, eps, 0.5, M._p(y), H * V, tt, H, V, ctx.act, ctx.stream), "k"))
-        add("  of which seq_diff_combine_kernel (difference of the maps + unit RMS)", tt, t, tt * H * V * (8 + es))
+        add("  seq_diff_combine_kernel alone (the read-out as a kernel of its own: prompt portions)", tt, t, tt * H * V * (8 + es))
         gate = torch.randn(tt, H, device=device).to(dt)
         bB = S.AttnArgs(q=M._p(qr), k_new=M._p(kr), v_new=M._p(vn), ldv=G * V, cache_k=M._p(ck), cache_v=M._p(cv), meta=M._p(meta), gate=M._p(gate), ldg=H,
                         out=M._p(y), ldo=H * V, scale=att.scale, softcap=0.0, out_mult=1.0, has_sink=1, block=att.max_positions, T=tt, heads=H, kv_heads=G,

@@ -45,15 +45,16 @@ def test_argument_blocks_match_the_header(tmp_path):
     from lit_llama_b200 import _seqlib as S
 
     prog = tmp_path / "layout.c"
-    prog.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b2l_seq.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", '
+    prog.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b2l_seq.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", '
                     "sizeof(b2l_seq_conv_rope_args), offsetof(b2l_seq_conv_rope_args, w), offsetof(b2l_seq_conv_rope_args, freq), "
                     "offsetof(b2l_seq_conv_rope_args, rot_mult), offsetof(b2l_seq_conv_rope_args, act_dtype), sizeof(b2l_seq_attn_args), "
-                    "offsetof(b2l_seq_attn_args, no_append), sizeof(b2l_seq_latent_attn_args), offsetof(b2l_seq_latent_attn_args, window));return 0;}\n")
+                    "offsetof(b2l_seq_attn_args, no_append), offsetof(b2l_seq_attn_args, diff_mult), sizeof(b2l_seq_latent_attn_args), "
+                    "offsetof(b2l_seq_latent_attn_args, window));return 0;}\n")
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)], check=True)
     out = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     A, B, L = S.ConvRopeArgs, S.AttnArgs, S.LatentAttnArgs
-    assert out == [C.sizeof(A), A.w.offset, A.freq.offset, A.rot_mult.offset, A.act_dtype.offset, C.sizeof(B), B.no_append.offset, C.sizeof(L),
+    assert out == [C.sizeof(A), A.w.offset, A.freq.offset, A.rot_mult.offset, A.act_dtype.offset, C.sizeof(B), B.no_append.offset, B.diff_mult.offset, C.sizeof(L),
                    L.window.offset]
 
 
