@@ -30,10 +30,10 @@ SIZES = {
 
 def rinirax_config(width, layers, heads, kv_heads, dim, vdim, conv, gru, l_heads, l_dim, l_rot, l_vdim, q_rank, kv_rank, window, ff, experts, top, groups,
                    keep, eff, vocab) -> dict:
-    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "diff": 0.5, "scale": dim ** -0.5, "rot": {"base": 2e4, "dims": dim}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "diff": 0.4, "scale": dim ** -0.5, "rot": {"base": 1e5, "dims": dim}}
     lat = {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": (l_dim + l_rot) ** -0.5,
-           "mask": {"size": window}, "rot": {"base": 5e5, "dims": l_rot, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
-    routed = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": groups, "keep": keep}}}
+           "mask": {"size": window}, "rot": {"base": 1e6, "dims": l_rot, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    routed = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}}}
     out = []
     for i in range(layers):
         k = i % 5
@@ -126,12 +126,12 @@ def kernel_table(model, engine, T: int, device, timer, peaks: dict) -> List[dict
         bA = S.AttnArgs(q=M._p(qr), k_new=M._p(kr), v_new=M._p(vn), ldv=G * V, cache_k=M._p(ck), cache_v=M._p(cv), meta=M._p(meta), gate=None, ldg=0,
                         out=M._p(maps), ldo=H * 2 * V, scale=att.scale, softcap=0.0, out_mult=1.0, has_sink=0, block=att.max_positions, T=tt, heads=2 * H,
                         kv_heads=G, K=K, V=V, act_dtype=ctx.act, window=0, gate_per_channel=0, maps=2, out_f32=1, no_append=0, diff_out=M._p(y), ldd=H * V,
-                        diff_lambda=att.lam, diff_eps=eps, diff_mult=0.5)
+                        diff_lambda=att.lam, diff_eps=eps, diff_mult=1.0 - att.diff)
         t = timer(lambda: M.local_attention(bA, ctx))
         nb = tt * (H * 2 * K * 4 + G * (2 * K + V) * es * 2 + H * V * es) + (keys * G * (2 * K + V) * es if tt == 1 else 0)
         add("seq_block_attention (2 maps per head + differential read-out) + append", tt, t, nb, 2.0 * tt * 2 * H * keys * (K + V),
             f"f32 scores on CUDA cores, {keys:.0f} keys per query")
-        t = timer(lambda: S.check(lib.b2l_seq_diff_combine(M._p(maps), H * 2 * V, att.lam, eps, 0.5, M._p(y), H * V, tt, H, V, ctx.act, ctx.stream), "k"))
+        t = timer(lambda: S.check(lib.b2l_seq_diff_combine(M._p(maps), H * 2 * V, att.lam, eps, 1.0 - att.diff, M._p(y), H * V, tt, H, V, ctx.act, ctx.stream), "k"))
         add("  seq_diff_combine_kernel alone (the read-out as a kernel of its own: prompt portions)", tt, t, tt * H * V * (8 + es))
         gate = torch.randn(tt, H, device=device).to(dt)
         bB = S.AttnArgs(q=M._p(qr), k_new=M._p(kr), v_new=M._p(vn), ldv=G * V, cache_k=M._p(ck), cache_v=M._p(cv), meta=M._p(meta), gate=M._p(gate), ldg=H,

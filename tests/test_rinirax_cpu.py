@@ -17,7 +17,7 @@ def small_config():
     att = {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 6, "scale": 0.3, "diff": 0.4, "conv": 3, "rot": {"base": 100.0, "dims": 4}}
     lat = {"heads": 2, "dim": 8, "rot_dim": 4, "vdim": 6, "q_rank": 10, "kv_rank": 12, "scale": 0.3, "mask": {"size": 5},
            "rot": {"base": 100.0, "dims": 4, "scaling": {"factor": 2.0, "original": 16, "fast": 4.0, "slow": 1.0}}}
-    experts = {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 6, "top": 2, "scale": 1.5, "groups": {"count": 3, "keep": 2}}}
+    experts = {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 6, "top": 2, "scale": 1.25, "groups": {"count": 3, "keep": 2}}}
     return {"architecture": "Rinirax", "vocab": 30, "width": 16, "norm": {"eps": 1e-5},
             "layers": [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": 20}},
                        {"type": "mingru", "mixer": {"width": 12}, "mlp": experts},
@@ -61,7 +61,7 @@ def test_argument_blocks_match_the_header(tmp_path):
 def test_oracle_rotation_frequencies_match_the_package():
     from lit_llama_b200.mixers import rope_frequencies
 
-    for dims, base, scaling in ((8, 100.0, None), (32, 5e5, {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}),
+    for dims, base, scaling in ((8, 100.0, None), (32, 3e5, {"factor": 6.0, "original": 512, "fast": 24.0, "slow": 1.0}),
                                 (16, 1e4, {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0})):
         f, mult = O.yarn_frequencies(dims, base, scaling)
         g, m = rope_frequencies(dims, base, scaling)
